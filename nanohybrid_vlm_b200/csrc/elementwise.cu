@@ -1,0 +1,188 @@
+// Row-wise kernels: embedding gather, RMSNorm (plain, with fused residual add, with row
+// gather), SiLU-and-multiply, and the error string shared by the whole library.
+//
+// Formulas follow nanovllm/layers/layernorm.py:16-40 (statistics in fp32, cast to the
+// storage type, then multiply by the weight in the storage type; the residual sum is
+// rounded once for the new residual while the norm uses the unrounded sum),
+// nanovllm/layers/activation.py:9-11 and nanovllm/layers/embed_head.py:38.
+#include <stdarg.h>
+#include <string.h>
+
+#include "nhv_common.cuh"
+
+static thread_local char g_error[512] = "";
+
+void nhv_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+NHV_API const char* nhv_last_error() { return g_error; }
+NHV_API int nhv_abi_version() { return 1; }
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
+                             int width, int vocab) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  const T* src = table + (size_t)(ok ? id : 0) * width;
+  T* dst = out + (size_t)t * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = ok ? src[c] : from_f32<T>(0.f);
+}
+
+NHV_API int nhv_embed(int dtype, void* out, const void* table, const int* ids, int n_tokens, int width, int vocab,
+                      cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  NHV_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embed: bad sizes");
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == NHV_F32)
+    embed_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)out, (const float*)table, ids, width, vocab);
+  else if (dtype == NHV_BF16)
+    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)table,
+                                                                 ids, width, vocab);
+  else
+    NHV_REQUIRE(false, "embed: unknown dtype %d", dtype);
+  NHV_CHECK_LAUNCH("embed");
+  return 0;
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One block per output row.  Row r reads source row rows[r] (or r when rows is null).
+// residual != null: s = x + residual in fp32; if write_residual the rounded s replaces residual.
+// The row of fp32 sums lives in shared memory between the two passes.
+template <typename T>
+__global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, T* __restrict__ residual,
+                               const T* __restrict__ w, const int* __restrict__ rows, int width, float eps,
+                               int write_residual, float weight_offset) {
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const size_t src = (size_t)(rows ? rows[r] : r) * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float s = to_f32<T>(x[src + c]);
+    if (residual) {
+      s += to_f32<T>(residual[src + c]);
+      if (write_residual) residual[src + c] = from_f32<T>(s);
+    }
+    row[c] = s;
+    ss = fmaf(s, s, ss);
+  }
+  const float total = block_sum(ss, red);
+  const float rstd = 1.0f / sqrtf(total / (float)width + eps);
+  T* dst = out + (size_t)r * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float n = round_to<T>(row[c] * rstd);
+    dst[c] = from_f32<T>(n * (to_f32<T>(w[c]) + weight_offset));
+  }
+}
+
+NHV_API int nhv_rmsnorm(int dtype, void* out, const void* x, void* residual, const void* w, const int* rows,
+                        int n_rows, int width, float eps, int write_residual, float weight_offset,
+                        cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NHV_REQUIRE(n_rows > 0 && width > 0, "rmsnorm: bad sizes");
+  const size_t smem = (size_t)width * sizeof(float);
+  NHV_REQUIRE(smem <= 200 * 1024, "rmsnorm: width %d is beyond the %d floats a row buffer holds", width,
+              200 * 1024 / 4);
+  NHV_REQUIRE(!(rows && residual && write_residual), "rmsnorm: a gathered norm cannot write the residual back");
+  int threads = 32;
+  while (threads < 1024 && threads * 4 < width) threads <<= 1;
+#define LAUNCH(T)                                                                                          \
+  do {                                                                                                     \
+    if (smem > 48 * 1024)                                                                                  \
+      NHV_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                    (int)smem), "rmsnorm");                                                \
+    rmsnorm_kernel<T><<<n_rows, threads, smem, stream>>>((T*)out, (const T*)x, (T*)residual, (const T*)w,  \
+                                                        rows, width, eps, write_residual, weight_offset); \
+  } while (0)
+  if (dtype == NHV_F32) LAUNCH(float);
+  else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
+  else NHV_REQUIRE(false, "rmsnorm: unknown dtype %d", dtype);
+#undef LAUNCH
+  NHV_CHECK_LAUNCH("rmsnorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+// gate_up [n, 2*inter] with gate in the first half of each row; out [n, inter].
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter;
+    const int c = (int)(i - t * inter);
+    const float g = to_f32<T>(gate_up[t * 2 * inter + c]);
+    const float u = to_f32<T>(gate_up[t * 2 * inter + inter + c]);
+    out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+// bf16, inter a multiple of 8: 16-byte loads and stores.
+__global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
+                                       int inter8, size_t total8) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter8;
+    const int c = (int)(i - t * inter8);
+    const uint4 gv = reinterpret_cast<const uint4*>(gate_up)[t * 2 * inter8 + c];
+    const uint4 uv = reinterpret_cast<const uint4*>(gate_up)[t * 2 * inter8 + inter8 + c];
+    const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&gv);
+    const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uv);
+    uint4 ov;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gf = __bfloat162float(g[k]);
+      o[k] = __float2bfloat16_rn(gf / (1.0f + expf(-gf)) * __bfloat162float(u[k]));
+    }
+    reinterpret_cast<uint4*>(out)[i] = ov;
+  }
+}
+
+NHV_API int nhv_silu_mul(int dtype, void* out, const void* gate_up, int n_rows, int inter, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NHV_REQUIRE(n_rows > 0 && inter > 0, "silu_mul: bad sizes");
+  const size_t total = (size_t)n_rows * inter;
+  const int threads = 256;
+  if (dtype == NHV_BF16 && inter % 8 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)gate_up % 16 == 0)) {
+    const size_t total8 = total / 8;
+    const int blocks = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
+    silu_mul_bf16x8_kernel<<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,
+                                                          inter / 8, total8);
+  } else {
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == NHV_F32)
+      silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+    else if (dtype == NHV_BF16)
+      silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out,
+                                                                    (const __nv_bfloat16*)gate_up, inter, total);
+    else
+      NHV_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
+  }
+  NHV_CHECK_LAUNCH("silu_mul");
+  return 0;
+}
+
+// ---------------------------------------------------------------- storage type -> fp32 rows
+template <typename T>
+__global__ void to_f32_kernel(float* __restrict__ out, const T* __restrict__ x, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = to_f32<T>(x[i]);
+}
+
+NHV_API int nhv_to_f32(int dtype, float* out, const void* x, size_t total, cudaStream_t stream) {
+  if (total == 0) return 0;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == NHV_BF16)
+    to_f32_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(out, (const __nv_bfloat16*)x, total);
+  else if (dtype == NHV_F32)
+    to_f32_kernel<float><<<blocks, threads, 0, stream>>>(out, (const float*)x, total);
+  else
+    NHV_REQUIRE(false, "to_f32: unknown dtype %d", dtype);
+  NHV_CHECK_LAUNCH("to_f32");
+  return 0;
+}

@@ -1,0 +1,81 @@
+// Shared helpers for the sm_100a kernels of this engine.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and the
+// CUDA stream to launch on, allocates nothing and returns 0 or an error code; the text
+// of the last error is read with nhv_last_error().  Python binds them with ctypes.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define NHV_API extern "C" __attribute__((visibility("default")))
+
+enum NhvDtype { NHV_F32 = 0, NHV_BF16 = 1 };
+
+// Defined in elementwise.cu.
+void nhv_set_error(const char* fmt, ...);
+
+#define NHV_REQUIRE(cond, ...)                                  \
+  do {                                                          \
+    if (!(cond)) {                                              \
+      nhv_set_error(__VA_ARGS__);                               \
+      return 1;                                                 \
+    }                                                           \
+  } while (0)
+
+#define NHV_CHECK_LAUNCH(name)                                                        \
+  do {                                                                                \
+    cudaError_t e_ = cudaPeekAtLastError();                                           \
+    if (e_ != cudaSuccess) {                                                          \
+      nhv_set_error("%s: launch failed: %s", name, cudaGetErrorString(e_));           \
+      return 2;                                                                       \
+    }                                                                                 \
+  } while (0)
+
+#define NHV_CUDA(call, name)                                                          \
+  do {                                                                                \
+    cudaError_t e_ = (call);                                                          \
+    if (e_ != cudaSuccess) {                                                          \
+      nhv_set_error("%s: %s", name, cudaGetErrorString(e_));                          \
+      return 2;                                                                       \
+    }                                                                                 \
+  } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Round a float to the storage type and back: the value the next op would read.
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32<T>(from_f32<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}

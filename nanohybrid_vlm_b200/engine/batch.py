@@ -1,0 +1,161 @@
+"""One step's batch: (request, its next tokens) for several requests, packed.
+
+A :class:`StepItem` says: these are the next tokens of that request, ``start`` tokens of it
+are already in the cache, and the logits at the places ``want`` among them are asked for.
+Prompt portions and single decoded tokens sit side by side; the only difference between
+them is the number of tokens.  (The reference builds two kinds of batch and never mixes
+them, nanovllm/engine/model_runner.py:924-1146,2029-2033.)
+
+:class:`BatchBuilder` turns items into the device arrays that kernels index: everything
+is written into ONE pinned host buffer and crosses to the device in one copy.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepItem:
+    req_id: object
+    tokens: list[int]
+    start: int                      # tokens of this request already in the cache = position of tokens[0]
+    want: list[int] = field(default_factory=list)   # places among `tokens` whose logits are wanted
+
+
+@dataclass
+class GroupTables:
+    block_tables: torch.Tensor      # [S, width] int32, -1 where there is no page
+    slot_mapping: torch.Tensor      # [T] int32: page * page_size + offset of every token of the step
+
+
+@dataclass
+class StepBatch:
+    n_tokens: int
+    n_seqs: int
+    n_logit_rows: int
+    token_ids: torch.Tensor         # [T] int32
+    positions: torch.Tensor         # [T] int32, position of each token in its own request
+    cu_q: torch.Tensor              # [S+1] int32, where each request's tokens start in the packed arrays
+    kv_len: torch.Tensor            # [S] int32, tokens of the request in the cache after this step
+    q_start: torch.Tensor           # [S] int32, kv_len minus this step's tokens
+    state_slots: torch.Tensor       # [S] int32, slot of fixed-size state (-1: none)
+    logit_rows: torch.Tensor        # [R] int32, rows of the packed arrays whose logits are wanted
+    groups: list[GroupTables]
+    # the same facts on the host, for parts that plan their launches from them
+    host_cu_q: list[int] = field(default_factory=list)
+    host_kv_len: list[int] = field(default_factory=list)
+    max_new_tokens: int = 0
+    max_kv_len: int = 0
+    decode_only: bool = False
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+class BatchBuilder:
+    def __init__(self, cache_manager, vocab_size: int, device, max_tokens: int, max_seqs: int, max_pages_per_seq: int):
+        self.cm = cache_manager
+        self.vocab = vocab_size
+        self.device = torch.device(device)
+        self.page_size = cache_manager.page_size
+        self.n_groups = len(cache_manager.groups)
+        self.max_tokens, self.max_seqs, self.max_pages = max_tokens, max_seqs, max_pages_per_seq
+        cap = self._layout(max_tokens, max_seqs, max_tokens, max_pages_per_seq)[1]
+        self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        self._np = self._host.numpy()
+        self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self.bytes_last_copy = 0
+        # the host buffer is written again at the next step: wait until the last copy has read it
+        self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
+
+    def _layout(self, T: int, S: int, R: int, width: int):
+        off, sections = 0, {}
+        for name, n in (("token_ids", T), ("positions", T), ("cu_q", S + 1), ("kv_len", S), ("q_start", S),
+                        ("state_slots", S), ("logit_rows", R)):
+            sections[name] = (off, n)
+            off += _align(n)
+        for g in range(self.n_groups):
+            sections[f"slots{g}"] = (off, T)
+            off += _align(T)
+            sections[f"tables{g}"] = (off, S * width)
+            off += _align(S * width)
+        return sections, off
+
+    def build(self, items: list[StepItem], table_width: int | None = None) -> StepBatch:
+        S = len(items)
+        T = sum(len(it.tokens) for it in items)
+        R = sum(len(it.want) for it in items)
+        if S == 0 or T == 0:
+            raise ValueError("a step needs at least one request with at least one token")
+        if S > self.max_seqs or T > self.max_tokens:
+            raise ValueError(f"step of {S} requests / {T} tokens is beyond the limits {self.max_seqs} / {self.max_tokens}")
+        ps = self.page_size
+        width = table_width or max(1, max(-(-(it.start + len(it.tokens)) // ps) for it in items))
+        if width > self.max_pages:
+            raise ValueError(f"a request needs {width} pages, beyond the limit of {self.max_pages}")
+        sec, total = self._layout(T, S, R, width)
+        if self._copied is not None:
+            self._copied.synchronize()
+        buf = self._np
+
+        def view(name):
+            o, n = sec[name]
+            return buf[o:o + n]
+
+        tok, pos = view("token_ids"), view("positions")
+        cu, kvl, qs, st, rows = view("cu_q"), view("kv_len"), view("q_start"), view("state_slots"), view("logit_rows")
+        slot_views = [view(f"slots{g}") for g in range(self.n_groups)]
+        table_views = [view(f"tables{g}").reshape(S, width) for g in range(self.n_groups)]
+        for tv in table_views:
+            tv.fill(-1)
+        t = r = 0
+        cu[0] = 0
+        for s, it in enumerate(items):
+            n = len(it.tokens)
+            if n == 0:
+                raise ValueError(f"request {it.req_id!r} brings no token")
+            end = it.start + n
+            if self.cm.num_tokens(it.req_id) < end:
+                raise RuntimeError(f"request {it.req_id!r}: pages cover {self.cm.num_tokens(it.req_id)} tokens, "
+                                   f"the step needs {end}")
+            tok[t:t + n] = it.tokens
+            p = np.arange(it.start, end, dtype=np.int32)
+            pos[t:t + n] = p
+            cu[s + 1] = t + n
+            kvl[s], qs[s] = end, it.start
+            slot = self.cm.state_slot(it.req_id)
+            st[s] = -1 if slot is None else slot
+            for w in it.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {it.req_id!r}: wanted place {w} is not among its {n} tokens")
+                rows[r] = t + w
+                r += 1
+            for g in range(self.n_groups):
+                table = np.asarray(self.cm.block_table(it.req_id, g), dtype=np.int32)
+                table_views[g][s, :min(len(table), width)] = table[:width]
+                pages = table[p // ps]
+                slot_views[g][t:t + n] = np.where(pages >= 0, pages * ps + p % ps, -1)
+            t += n
+        if tok[:T].min() < 0 or tok[:T].max() >= self.vocab:
+            raise ValueError(f"token ids must lie in [0, {self.vocab})")
+        self._dev[:total].copy_(self._host[:total], non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+        self.bytes_last_copy = total * 4
+
+        def dev(name):
+            o, n = sec[name]
+            return self._dev[o:o + n]
+
+        groups = [GroupTables(dev(f"tables{g}").view(S, width), dev(f"slots{g}")) for g in range(self.n_groups)]
+        lens = [len(it.tokens) for it in items]
+        return StepBatch(
+            n_tokens=T, n_seqs=S, n_logit_rows=R, token_ids=dev("token_ids"), positions=dev("positions"),
+            cu_q=dev("cu_q"), kv_len=dev("kv_len"), q_start=dev("q_start"), state_slots=dev("state_slots"),
+            logit_rows=dev("logit_rows"), groups=groups, host_cu_q=[int(x) for x in cu[:S + 1]],
+            host_kv_len=[it.start + n for it, n in zip(items, lens)], max_new_tokens=max(lens),
+            max_kv_len=max(it.start + n for it, n in zip(items, lens)), decode_only=max(lens) == 1)

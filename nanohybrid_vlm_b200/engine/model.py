@@ -1,0 +1,116 @@
+"""A causal language model put together from a :class:`ModelSpec`.
+
+It builds the parts, lists every tensor they own with the checkpoint tensors that fill it,
+and runs one step over a packed batch: embed, the layer runs in the order the spec gives,
+the final norm at the wanted rows only, the head.  It is the same object for every
+architecture; what differs is the spec.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, CacheView, FixedStateNeed, PagedKVNeed, Part
+from ..parts.embedding import LMHead, TokenEmbedding
+from ..parts.spec import ModelSpec, ParamDecl, PartUse, Source
+
+
+@dataclass(frozen=True)
+class BoundParam:
+    """A tensor of the model: its full name, declaration (sources carry full checkpoint names) and owner."""
+    name: str
+    decl: ParamDecl
+    owner: Part
+    local: str
+
+
+class CausalLM:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device):
+        spec.validate()
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device)
+        env = self.env = BuildEnv(spec.hidden_size, dtype, device, spec.max_position)
+        self._uses: list[tuple[PartUse, Part]] = []
+
+        def build(registry, use: PartUse):
+            obj = registry.get(use.spec.kind)(use.spec, env)
+            self._uses.append((use, obj))
+            return obj
+
+        self.embedding = TokenEmbedding(spec.embedding.spec, env)
+        self._uses.append((spec.embedding, self.embedding))
+        self.blocks = []
+        for layer in spec.layers:
+            mixer = build(MIXERS, layer.mixer)
+            mixer_norm = build(NORMS, layer.mixer_norm)
+            ffn = build(FEED_FORWARDS, layer.ffn)
+            ffn_norm = build(NORMS, layer.ffn_norm)
+            self.blocks.append(BLOCKS.get(layer.block.kind)(layer.block, mixer, mixer_norm, ffn, ffn_norm))
+        self.final_norm = build(NORMS, spec.final_norm)
+        self.head = LMHead(spec.head.spec, env)
+        self._uses.append((spec.head, self.head))
+        self.positions = list(env._positions.values())
+
+    # ------------------------------------------------------------------ tensors
+    def param_table(self) -> list[BoundParam]:
+        table, seen = [], set()
+        for use, obj in self._uses:
+            for decl in obj.params():
+                full = use.prefix + decl.name
+                if full in seen:
+                    raise ValueError(f"two parts declare the tensor {full!r}")
+                seen.add(full)
+                srcs = tuple(Source(use.prefix + s.name, s.row, s.rows) for s in decl.resolved_sources())
+                table.append(BoundParam(full, ParamDecl(decl.name, decl.shape, decl.init, decl.storage, srcs), obj,
+                                        decl.name))
+        return table
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Hand every part its tensors (``tensors`` is keyed by full names)."""
+        per_part: dict[int, dict[str, torch.Tensor]] = {}
+        owners = {}
+        for bp in self.param_table():
+            if bp.name not in tensors:
+                raise KeyError(f"no tensor for {bp.name}")
+            per_part.setdefault(id(bp.owner), {})[bp.local] = tensors[bp.name]
+            owners[id(bp.owner)] = bp.owner
+        for key, owner in owners.items():
+            owner.bind(per_part[key])
+        if self.head.tied:
+            self.head.tie(self.embedding.w_weight)
+        self.tensors = tensors
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.tensors.values())
+
+    # ------------------------------------------------------------------ cache needs
+    def cache_needs(self) -> list[PagedKVNeed | FixedStateNeed | None]:
+        """For every run of the order: what its mixer keeps between steps (None: nothing, or it reads
+        another run's cache)."""
+        needs = []
+        for run in self.spec.order:
+            need = self.blocks[run.layer].mixer.cache_need()
+            if run.cache_from is not None:
+                src = self.blocks[self.spec.order[run.cache_from].layer].mixer.cache_need()
+                if need != src:
+                    raise ValueError(f"a run reads the cache of run {run.cache_from}, whose shape differs from its own")
+                need = None
+            needs.append(need)
+        return needs
+
+    # ------------------------------------------------------------------ one step
+    def forward(self, batch, storage) -> torch.Tensor:
+        """Run the batch's tokens through every layer run; returns fp32 logits [wanted rows, vocab]."""
+        h = self.embedding.forward(batch.token_ids)
+        for pos in self.positions:
+            h = pos.add_to_embeddings(h, batch)
+        residual = None
+        for i, run in enumerate(self.spec.order):
+            view = storage.view(i, run.cache_from, batch)
+            h, residual = self.blocks[run.layer].forward(h, residual, batch, view)
+        if batch.n_logit_rows == 0:
+            return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=self.device)
+        x = self.final_norm.forward_add_rows(h, residual, batch.logit_rows)
+        return self.head.forward(x)

@@ -1,0 +1,101 @@
+"""The model runner: the model, its cache and the one step function.
+
+``step(items)`` runs exactly the tokens it is given, as one batch, from the cache that
+earlier steps left, and returns fp32 logits at the wanted places.  Generation
+(:mod:`.llm_engine`) and trace replay (``bin/trace_run``) both drive this object; neither
+has a forward pass, a cache or a loader of its own.  The reference's counterpart is
+nanovllm/engine/model_runner.py (init :39-258, cache sizing :650-916, run :2017-2058).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import CacheLayout, CacheManager, CacheStorage
+from ..config import Config
+from ..kernels import library, ops
+from ..weights import load_weights, materialize_random
+from .batch import BatchBuilder, StepItem
+from .model import CausalLM
+
+
+class ModelRunner:
+    def __init__(self, config: Config, *, random_weights_seed: int | None = None, device: str = "cuda:0"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this engine computes on a B200 only and has no CPU fallback")
+        library()   # compile / load the kernels now; fail loudly if that is impossible
+        self.config = config
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.dtype = config.dtype
+        spec = config.architecture.build_spec(config.model_config)
+        self.model = CausalLM(spec, self.dtype, self.device)
+        if random_weights_seed is None:
+            load_weights(self.model, config.model)
+        else:
+            materialize_random(self.model, random_weights_seed)
+        self.vocab_size = spec.vocab_size
+
+        self.layout = CacheLayout.from_needs(self.model.cache_needs())
+        self.page_size = config.kvcache_block_size
+        self.max_pages_per_seq = -(-config.max_model_len // self.page_size)
+        num_slots = config.num_state_slots
+        if num_slots < 0:
+            num_slots = config.max_num_seqs if self.layout.needs_state_slots else 0
+        num_pages = self._size_pools(num_slots)
+        config.num_kvcache_blocks, config.num_state_slots = num_pages, num_slots
+        counts = [num_pages] * len(self.layout.groups)
+        self.cache = CacheManager(self.layout.groups, self.page_size, counts, num_slots)
+        self.storage = CacheStorage(self.layout, spec.order, self.page_size, counts, num_slots, self.dtype, self.device)
+        self.builder = BatchBuilder(self.cache, self.vocab_size, self.device,
+                                    max_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,
+                                    max_pages_per_seq=self.max_pages_per_seq)
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ sizing
+    def _activation_allowance(self) -> int:
+        """A generous bound on what one step's intermediate tensors take."""
+        item = 2 if self.dtype == torch.bfloat16 else 4
+        widest = max((d.shape[0] for bp in self.model.param_table() for d in [bp.decl] if len(d.shape) == 2
+                      and d.shape[0] != self.vocab_size), default=self.model.spec.hidden_size)
+        T = self.config.max_num_batched_tokens
+        per_token = (3 * widest + 6 * self.model.spec.hidden_size) * item
+        logits = self.config.max_num_seqs * self.vocab_size * (4 + item)
+        return 2 * T * per_token + 2 * logits + (256 << 20)
+
+    def _size_pools(self, num_slots: int) -> int:
+        cfg = self.config
+        per_page = sum(self.layout.page_bytes(self.page_size, self.dtype))
+        useful = cfg.max_num_seqs * self.max_pages_per_seq       # more pages than this can never be held
+        if cfg.num_kvcache_blocks > 0:
+            return cfg.num_kvcache_blocks
+        if per_page == 0:
+            return 0
+        free, total = torch.cuda.mem_get_info(self.device)
+        used = total - free
+        budget = int(total * cfg.gpu_memory_utilization) - used - self._activation_allowance()
+        budget -= num_slots * self.layout.state_bytes_per_slot(self.dtype)
+        pages = min(budget // per_page, useful)
+        if pages < self.max_pages_per_seq:
+            raise RuntimeError(f"not enough device memory for the cache: room for {max(pages, 0)} pages of "
+                               f"{per_page} bytes, one request of max_model_len needs {self.max_pages_per_seq}")
+        return int(pages)
+
+    # ------------------------------------------------------------------ the step
+    @torch.no_grad()
+    def step(self, items: list[StepItem]) -> torch.Tensor:
+        """Run the items' tokens as one batch; fp32 logits [number of wanted places, vocab] on the device,
+        in the order of the items and of each item's ``want``."""
+        batch = self.builder.build(items)
+        return self.model.forward(batch, self.storage)
+
+    @torch.no_grad()
+    def sample(self, logits: torch.Tensor, temperatures, seeds, positions) -> list[int]:
+        """One token per logits row; host lists in, host list out."""
+        n = logits.shape[0]
+        dev = self.device
+        t = torch.tensor(temperatures, dtype=torch.float32).pin_memory().to(dev, non_blocking=True)
+        s = torch.tensor(seeds, dtype=torch.int64).pin_memory().to(dev, non_blocking=True)
+        p = torch.tensor(positions, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+        out = torch.empty(n, dtype=torch.int32, device=dev)
+        ops.sample(out, logits, t, s, p)
+        return out.tolist()

@@ -1,0 +1,161 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees.  It decides; the cache manager keeps the books and the runner computes.
+
+Policy, after nanovllm/engine/scheduler.py (queues :133-134, budget :544-547, portions
+:836-839, preemption :350-378,492-514,906-949, no progress :898-903, finishing :972-983):
+
+* ``waiting`` holds new, partly prefilled and preempted requests, first come first served;
+  ``running`` holds requests whose prompt is done.
+* One step = one mixed batch.  Running requests get one token each first ("decode_first");
+  what is left of ``max_num_batched_tokens`` goes to the head of ``waiting``, whose prompt is
+  cut where the budget ends and goes on from there in the next step.  With
+  "prefill_first" nothing decodes while a request waits.
+* A request is admitted only if pages for all its current tokens (and a state slot, if the
+  model needs one) are free and fewer than ``max_num_seqs`` requests are live; else the
+  queue waits behind it.
+* When a decoding request needs a page and none is free, the running request with the
+  least computed tokens (ties: the oldest) that is not yet part of this step is
+  preempted: its pages go back, it returns to the tail of ``waiting`` and is later
+  recomputed from its first token, generated tokens included.  If there is no other, the
+  request preempts itself.
+* A step that can schedule nothing raises: the engine would spin.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..cache import CacheManager
+from .sequence import Sequence, SequenceStatus
+
+
+@dataclass
+class SchedulePlan:
+    seqs: list[Sequence] = field(default_factory=list)     # in batch order; seq.num_scheduled_tokens is set
+    num_decode_tokens: int = 0
+    num_prefill_tokens: int = 0
+    preempted_seq_ids: list[int] = field(default_factory=list)
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, *, max_num_seqs: int, max_num_batched_tokens: int, max_model_len: int,
+                 eos: int = -1, policy: str = "decode_first", max_portion: int | None = None):
+        self.cache = cache
+        self.max_num_seqs = max_num_seqs
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.max_model_len = max_model_len
+        self.eos = eos
+        self.policy = policy
+        self.max_portion = max_portion          # test hook: no portion of a prompt is longer than this
+        self.waiting: deque[Sequence] = deque()
+        self.running: deque[Sequence] = deque()
+        self.num_preemptions = 0
+        self.num_recomputed_tokens = 0
+
+    def is_finished(self) -> bool:
+        return not self.waiting and not self.running
+
+    def add(self, seq: Sequence) -> None:
+        if len(seq) >= self.max_model_len:
+            raise ValueError(f"prompt of {len(seq)} tokens leaves no room to generate within max_model_len "
+                             f"{self.max_model_len}")
+        most = min(len(seq) + seq.max_tokens, self.max_model_len)
+        for g, pool in enumerate(self.cache.pools):
+            if -(-most // self.cache.page_size) > pool.num_pages:
+                raise ValueError(f"request of up to {most} tokens can never fit the cache "
+                                 f"({pool.num_pages} pages of {self.cache.page_size} tokens)")
+        self.waiting.append(seq)
+
+    # ------------------------------------------------------------------ one step's plan
+    def schedule(self) -> SchedulePlan:
+        plan = SchedulePlan()
+        budget = self.max_num_batched_tokens
+        scheduled: set[int] = set()
+
+        if not (self.policy == "prefill_first" and self.waiting):
+            for seq in list(self.running):
+                if seq.status != SequenceStatus.RUNNING or budget == 0 or len(plan.seqs) >= self.max_num_seqs:
+                    continue
+                while not self.cache.can_allocate(seq.seq_id, len(seq)):
+                    victim = self._pick_victim(scheduled, exclude=seq)
+                    if victim is None:
+                        victim = seq
+                    self._preempt(victim, plan)
+                    if victim is seq:
+                        break
+                if seq.status != SequenceStatus.RUNNING:
+                    continue
+                self.cache.allocate(seq.seq_id, len(seq))
+                seq.num_scheduled_tokens = 1
+                plan.seqs.append(seq)
+                scheduled.add(seq.seq_id)
+                plan.num_decode_tokens += 1
+                budget -= 1
+
+        while self.waiting and budget > 0 and len(plan.seqs) < self.max_num_seqs:
+            seq = self.waiting[0]
+            if seq.seq_id not in self.cache:
+                live = self.cache.num_live()
+                if live >= self.max_num_seqs or not self.cache.can_allocate(seq.seq_id, len(seq)):
+                    break
+                self.cache.allocate(seq.seq_id, len(seq))
+            remaining = len(seq) - seq.num_cached_tokens
+            n = min(remaining, budget, self.max_portion or remaining)
+            seq.num_scheduled_tokens = n
+            plan.seqs.append(seq)
+            scheduled.add(seq.seq_id)
+            plan.num_prefill_tokens += n
+            budget -= n
+            if n == remaining:
+                self.waiting.popleft()
+                seq.status = SequenceStatus.RUNNING
+                self.running.append(seq)
+            else:
+                break   # a prompt was cut: the budget (or the portion limit) is used up for this step
+
+        if not plan.seqs:
+            raise RuntimeError("Scheduler cannot make progress: no request fits the free cache pages and budget "
+                               f"(waiting {len(self.waiting)}, running {len(self.running)}, free pages "
+                               f"{[p.num_free for p in self.cache.pools]})")
+        return plan
+
+    def _pick_victim(self, scheduled: set[int], exclude: Sequence) -> Sequence | None:
+        candidates = [s for s in self.running
+                      if s is not exclude and s.seq_id not in scheduled and s.status == SequenceStatus.RUNNING]
+        if not candidates:
+            return None
+        return min(candidates, key=lambda s: (s.num_cached_tokens, s.seq_id))
+
+    def _preempt(self, seq: Sequence, plan: SchedulePlan) -> None:
+        self.cache.free(seq.seq_id)
+        self.num_preemptions += 1
+        self.num_recomputed_tokens += seq.num_cached_tokens
+        seq.num_preemptions += 1
+        seq.num_cached_tokens = 0
+        seq.num_scheduled_tokens = 0
+        seq.status = SequenceStatus.WAITING
+        self.running.remove(seq)
+        self.waiting.append(seq)
+        plan.preempted_seq_ids.append(seq.seq_id)
+
+    # ------------------------------------------------------------------ after the step
+    def postprocess(self, seqs: list[Sequence], token_ids: list[int | None]) -> None:
+        """``token_ids[i]`` is the token chosen for ``seqs[i]``, or None if its portion did not reach the
+        end of the request (nothing was sampled for it)."""
+        for seq, token in zip(seqs, token_ids):
+            seq.num_cached_tokens += seq.num_scheduled_tokens
+            seq.num_scheduled_tokens = 0
+            if seq.num_cached_tokens < len(seq):
+                self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
+                continue
+            if token is None:
+                raise RuntimeError(f"request {seq.seq_id}: its last token was computed but no token was chosen")
+            seq.append_token(token)
+            done = (not seq.ignore_eos and token == self.eos) or seq.num_completion_tokens >= seq.max_tokens \
+                or len(seq) >= self.max_model_len
+            if done:
+                seq.status = SequenceStatus.FINISHED
+                self.cache.free(seq.seq_id)
+                self.running.remove(seq)
+            else:
+                self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)

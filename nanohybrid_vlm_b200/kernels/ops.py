@@ -1,0 +1,171 @@
+"""Tensor-level wrappers of the CUDA entry points.
+
+Each wrapper checks what its kernel assumes (device, dtype, contiguity, sizes) and then
+launches on the current CUDA stream.  Outputs are passed in by the caller, so a step can
+run from preallocated buffers.  bfloat16 matrix products go to cuBLAS through
+``torch.mm`` (the reference's own projections are library calls too,
+nanovllm/layers/linear.py:66); float32 products use this library's fixed-order kernel so
+that the 32-bit path never sees a reduced-precision matrix mode.
+"""
+from __future__ import annotations
+
+import torch
+
+from .library import KernelError, call
+
+F32, BF16 = 0, 1
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {t.dtype}")
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("this engine computes on the GPU only: got a CPU tensor (there is no CPU fallback)")
+
+
+def _contig(name: str, t: torch.Tensor) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    _need_cuda(out, table, ids)
+    _contig("out", out); _contig("table", table)
+    assert ids.dtype == torch.int32 and out.dtype == table.dtype and out.shape[1] == table.shape[1]
+    call("nhv_embed", dtype_code(out), out.data_ptr(), table.data_ptr(), ids.data_ptr(), ids.numel(),
+         table.shape[1], table.shape[0], stream_ptr())
+
+
+def rmsnorm(out, x, weight, eps: float, residual=None, rows=None, write_residual: bool = True,
+            weight_offset: float = 0.0) -> None:
+    """out[r] = norm(x[src] (+ residual[src])) * (weight + weight_offset), src = rows[r] or r.
+    With a residual and write_residual the rounded sum replaces residual[src]."""
+    _need_cuda(out, x, weight, residual, rows)
+    _contig("out", out); _contig("x", x)
+    width = x.shape[-1]
+    assert weight.numel() == width and weight.dtype == x.dtype and out.dtype == x.dtype
+    n_rows = rows.numel() if rows is not None else x.numel() // width
+    assert out.numel() == n_rows * width
+    if residual is not None:
+        _contig("residual", residual)
+        assert residual.shape == x.shape and residual.dtype == x.dtype
+    if rows is not None:
+        assert rows.dtype == torch.int32
+    call("nhv_rmsnorm", dtype_code(x), out.data_ptr(), x.data_ptr(), _ptr(residual), weight.data_ptr(), _ptr(rows),
+         n_rows, width, float(eps), int(bool(write_residual and residual is not None and rows is None)),
+         float(weight_offset), stream_ptr())
+
+
+def silu_mul(out, gate_up) -> None:
+    _need_cuda(out, gate_up)
+    _contig("out", out); _contig("gate_up", gate_up)
+    inter = gate_up.shape[-1] // 2
+    assert gate_up.shape[-1] == 2 * inter and out.shape[-1] == inter and out.dtype == gate_up.dtype
+    call("nhv_silu_mul", dtype_code(out), out.data_ptr(), gate_up.data_ptr(), out.numel() // inter, inter, stream_ptr())
+
+
+def to_f32(out, x) -> None:
+    _need_cuda(out, x)
+    _contig("out", out); _contig("x", x)
+    assert out.dtype == torch.float32 and out.numel() == x.numel()
+    call("nhv_to_f32", dtype_code(x), out.data_ptr(), x.data_ptr(), x.numel(), stream_ptr())
+
+
+def qk_norm_rope_store(qkv, q_out, kv_pages, slot_mapping, positions, q_weight, k_weight, cos_sin, rotary_dim: int,
+                       nq: int, nkv: int, head_dim: int, eps: float, weight_offset: float = 0.0) -> None:
+    """qkv [T, (nq+2nkv)*d] -> q_out [T, nq*d] (normed, rotated) and K/V rows in kv_pages
+    [pages, 2, nkv, page_size, d] at slot_mapping.  kv_pages None: queries only."""
+    _need_cuda(qkv, q_out, kv_pages, slot_mapping, positions, q_weight, k_weight, cos_sin)
+    assert qkv.stride(-1) == 1 and q_out.stride(-1) == 1 and qkv.dim() == 2 and q_out.dim() == 2
+    n_tokens = qkv.shape[0]
+    if kv_pages is not None:
+        _contig("kv_pages", kv_pages)
+        n_pages, two, h, page_size, d = kv_pages.shape
+        assert two == 2 and h == nkv and d == head_dim and kv_pages.dtype == qkv.dtype
+        assert slot_mapping.dtype == torch.int32 and slot_mapping.numel() >= n_tokens
+    else:
+        n_pages, page_size = 0, 0
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == rotary_dim
+        assert positions.dtype == torch.int32
+    call("nhv_qk_norm_rope_store", dtype_code(qkv), qkv.data_ptr(), qkv.stride(0), q_out.data_ptr(), q_out.stride(0),
+         _ptr(kv_pages), _ptr(slot_mapping), _ptr(positions), _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin),
+         int(rotary_dim), 0 if cos_sin is None else cos_sin.shape[0], n_tokens, nq, nkv, head_dim, page_size, n_pages,
+         float(eps), float(weight_offset), stream_ptr())
+
+
+def attention_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_tokens: int, nq: int, nkv: int,
+                   head_dim: int, scale: float, window: int = 0) -> None:
+    """Causal attention of this step's tokens over the pages: q [T, nq*d] -> out [T, nq*d]."""
+    _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len)
+    _contig("kv_pages", kv_pages)
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and out.dtype == q.dtype == kv_pages.dtype
+    n_pages, two, h, page_size, d = kv_pages.shape
+    assert two == 2 and h == nkv and d == head_dim
+    assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
+    assert cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
+    call("nhv_attention_simt", dtype_code(q), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
+         kv_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(),
+         n_seqs, n_tokens, nq, nkv, head_dim, page_size, n_pages, int(window), float(scale), stream_ptr())
+
+
+def attention(out, q, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """Attention of the step's tokens over the cache: picks the kernel for the dtype and sizes."""
+    attention_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
+                   nq, nkv, head_dim, scale, window)
+
+
+def linear(out, x, weight) -> None:
+    """out[M,N] = x[M,K] @ weight[N,K]^T.  out may be float32 while x and weight are bfloat16."""
+    _need_cuda(out, x, weight)
+    _contig("out", out); _contig("weight", weight)
+    assert x.dim() == 2 and weight.dim() == 2 and x.stride(1) == 1 and x.dtype == weight.dtype
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and out.shape == (M, N)
+    if x.dtype == torch.float32:
+        assert out.dtype == torch.float32
+        call("nhv_gemm_nt_simt", F32, out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K, N, 0,
+             stream_ptr())
+    elif out.dtype == torch.float32:
+        # the product is rounded to bfloat16 and then widened, as the reference's head does
+        # (nanovllm/layers/embed_head.py:61, nanovllm/layers/sampler.py:12)
+        tmp = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        torch.mm(x, weight.t(), out=tmp)
+        to_f32(out, tmp)
+    else:
+        torch.mm(x, weight.t(), out=out)
+
+
+def linear_simt(out, x, weight) -> None:
+    """The fixed-order CUDA-core product for any storage type (tests, and sizes a fast kernel refuses)."""
+    _need_cuda(out, x, weight)
+    M, K = x.shape
+    N = weight.shape[0]
+    call("nhv_gemm_nt_simt", dtype_code(x), out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K,
+         N, int(out.dtype == torch.float32 and x.dtype != torch.float32), stream_ptr())
+
+
+def sample(out, logits, temperatures, seeds, positions) -> None:
+    """out[r] = the token chosen from logits[r] (float32): argmax if temperatures[r] == 0, else the
+    exponential race with noise keyed by (seeds[r], positions[r])."""
+    _need_cuda(out, logits, temperatures, seeds, positions)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    assert temperatures.dtype == torch.float32 and seeds.dtype == torch.int64 and positions.dtype == torch.int32
+    call("nhv_sample", out.data_ptr(), logits.data_ptr(), logits.stride(0), temperatures.data_ptr(), seeds.data_ptr(),
+         positions.data_ptr(), logits.shape[0], logits.shape[1], stream_ptr())
