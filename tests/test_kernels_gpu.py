@@ -1,0 +1,268 @@
+"""Each kernel alone against a plain PyTorch fp32 reference of the same op, at sizes other than the
+engine's tiny models: widths and vocabularies that are no power of two, odd group sizes, head sizes
+in steps of 16, page sizes from 1 up, shuffled page tables."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from nanohybrid_vlm_b200.kernels import ops
+    return ops
+
+
+def dev(t):
+    return t.cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,vocab,n", [(96, 384, 7), (1000, 51, 33), (4096, 17, 3)])
+def test_embed(ops, dtype, width, vocab, n):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, width, generator=g).to(dtype)
+    ids = torch.randint(0, vocab, (n,), generator=g, dtype=torch.int32)
+    out = torch.empty(n, width, dtype=dtype, device="cuda")
+    ops.embed(out, dev(table), dev(ids))
+    assert torch.equal(out.cpu(), table[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,rows,eps", [(96, 5, 1e-5), (1000, 3, 1e-6), (4096, 9, 1e-6), (12290, 2, 1e-3)])
+def test_rmsnorm_and_fused_residual(ops, dtype, width, rows, eps):
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(rows, width, generator=g) * 3).to(dtype)
+    res = torch.randn(rows, width, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(width, generator=g)).to(dtype)
+    out = torch.empty(rows, width, dtype=dtype, device="cuda")
+    ops.rmsnorm(out, dev(x), dev(w), eps)
+    torch.testing.assert_close(out.cpu().float(), plain.rms_norm(x, w, eps).float(), **tol(dtype))
+    res_d = dev(res.clone())
+    ops.rmsnorm(out, dev(x), dev(w), eps, residual=res_d)
+    y, new_res = plain.add_rms_norm(x, res, w, eps)
+    torch.testing.assert_close(out.cpu().float(), y.float(), **tol(dtype))
+    torch.testing.assert_close(res_d.cpu().float(), new_res.float(), **tol(dtype))
+    # gathered rows, nothing written back
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32)
+    out2 = torch.empty(2, width, dtype=dtype, device="cuda")
+    res_d = dev(res.clone())
+    ops.rmsnorm(out2, dev(x), dev(w), eps, residual=res_d, rows=dev(idx), write_residual=False)
+    torch.testing.assert_close(out2.cpu().float(), y[idx.long()].float(), **tol(dtype))
+    assert torch.equal(res_d.cpu(), res)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter,rows", [(160, 5), (1001, 3), (12288, 4)])
+def test_silu_mul(ops, dtype, inter, rows):
+    g = torch.Generator().manual_seed(2)
+    gu = (torch.randn(rows, 2 * inter, generator=g) * 2).to(dtype)
+    out = torch.empty(rows, inter, dtype=dtype, device="cuda")
+    ops.silu_mul(out, dev(gu))
+    gf, uf = gu[:, :inter].float(), gu[:, inter:].float()
+    ref = (gf * torch.sigmoid(gf) * uf).to(dtype)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (5, 384, 96), (67, 130, 70), (130, 65, 257)])
+def test_gemm_simt(ops, dtype, M, N, K):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w = torch.randn(N, K, generator=g).to(dtype)
+    out = torch.empty(M, N, dtype=dtype, device="cuda")
+    ops.linear_simt(out, dev(x), dev(w))
+    ref = (x.double() @ w.double().t()).float()
+    t = dict(rtol=1e-5, atol=1e-4) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-1)
+    torch.testing.assert_close(out.cpu().float(), ref, **t)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
+    """A row's result is the same bits whatever else is in the batch."""
+    g = torch.Generator().manual_seed(4)
+    x = dev(torch.randn(77, 300, generator=g))
+    w = dev(torch.randn(190, 300, generator=g))
+    full = torch.empty(77, 190, device="cuda")
+    ops.linear_simt(full, x, w)
+    for rows in ([3], [10, 11], list(range(60, 77))):
+        sub = torch.empty(len(rows), 190, device="cuda")
+        ops.linear_simt(sub, x[rows].contiguous(), w)
+        assert torch.equal(sub, full[rows])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(3, 384, 96), (40, 1000, 256)])
+def test_linear(ops, dtype, M, N, K):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w = torch.randn(N, K, generator=g).to(dtype)
+    ref = (x.double() @ w.double().t()).float()
+    t = dict(rtol=1e-5, atol=1e-4) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-1)
+    out = torch.empty(M, N, dtype=dtype, device="cuda")
+    ops.linear(out, dev(x), dev(w))
+    torch.testing.assert_close(out.cpu().float(), ref, **t)
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.linear(out32, dev(x), dev(w))
+    torch.testing.assert_close(out32.cpu(), ref, **t)
+
+
+def make_pages(k, v, page_size, n_pages, rng, dtype):
+    """Scatter one request's keys/values [T, nkv, d] over shuffled pages. Returns pages tensor and table."""
+    T, nkv, d = k.shape
+    need = -(-T // page_size)
+    ids = rng.permutation(n_pages)[:need]
+    pages = torch.full((n_pages, 2, nkv, page_size, d), float("nan")).to(dtype)
+    for j in range(T):
+        pages[ids[j // page_size], 0, :, j % page_size] = k[j]
+        pages[ids[j // page_size], 1, :, j % page_size] = v[j]
+    return pages, ids
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot,page", [(4, 2, 16, 16, 16), (6, 2, 32, 32, 8), (3, 3, 48, 24, 1), (14, 2, 80, 80, 5),
+                                               (8, 1, 128, 128, 256), (2, 1, 256, 64, 32)])
+def test_qk_norm_rope_store(ops, dtype, nq, nkv, d, rot, page):
+    g = torch.Generator().manual_seed(6)
+    T, max_pos, eps, theta = 23, 300, 1e-5, 5000.0
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+    positions = torch.randint(0, max_pos, (T,), generator=g, dtype=torch.int32)
+    n_pages = -(-T // page) + 3
+    perm = torch.randperm(n_pages * page, generator=g)[:T].to(torch.int32)
+    perm[5] = -1                                      # a token that must not be stored
+    cos, sin = plain.rope_table(rot, max_pos, theta)
+    table = torch.cat((cos, sin), -1).contiguous()
+    q_out = torch.empty(T, nq * d, dtype=dtype, device="cuda")
+    pages = torch.zeros(n_pages, 2, nkv, page, d, dtype=dtype, device="cuda")
+    ops.qk_norm_rope_store(dev(qkv), q_out, pages, dev(perm), dev(positions), dev(qw), dev(kw), dev(table), rot,
+                           nq, nkv, d, eps)
+    q, k, v = qkv.split([nq * d, nkv * d, nkv * d], -1)
+    q, k, v = q.view(T, nq, d), k.view(T, nkv, d), v.view(T, nkv, d)
+
+    def rope_partial(x):
+        c, s = cos[positions.long()], sin[positions.long()]
+        return torch.cat((plain.apply_rope(x[..., :rot], c, s), x[..., rot:]), -1)
+
+    q_ref = rope_partial(plain.rms_norm(q, qw, eps))
+    k_ref = rope_partial(plain.rms_norm(k, kw, eps))
+    torch.testing.assert_close(q_out.cpu().float().view(T, nq, d), q_ref.float(), **tol(dtype))
+    pc = pages.cpu()
+    for t in range(T):
+        s = int(perm[t])
+        if s < 0:
+            continue
+        torch.testing.assert_close(pc[s // page, 0, :, s % page].float(), k_ref[t].float(), **tol(dtype))
+        assert torch.equal(pc[s // page, 1, :, s % page], v[t])
+    written = torch.zeros(n_pages * page, dtype=torch.bool)
+    written[perm[perm >= 0].long()] = True
+    flat = pc.permute(0, 3, 1, 2, 4).reshape(n_pages * page, -1)
+    assert (flat[~written] == 0).all(), "a slot that no token maps to was written"
+
+
+def reference_attention(q, k, v, scale, window):
+    """q [n_new, nq, d] at the last n_new positions of k/v [T, nkv, d]; fp64 softmax."""
+    T, nkv, d = k.shape
+    n_new, nq, _ = q.shape
+    G = nq // nkv
+    out = torch.empty(n_new, nq, d, dtype=torch.float64)
+    for i in range(n_new):
+        pos = T - n_new + i
+        lo = max(0, pos - window + 1) if window else 0
+        for h in range(nq):
+            s = (k[lo:pos + 1, h // G].double() @ q[i, h].double()) * scale
+            p = torch.softmax(s, 0)
+            out[i, h] = p @ v[lo:pos + 1, h // G].double()
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 16, 0), (6, 2, 32, 8, 0), (3, 3, 48, 1, 0),
+                                                  (14, 2, 80, 5, 0), (8, 1, 128, 64, 0), (18, 2, 64, 16, 0),
+                                                  (4, 2, 32, 8, 19), (2, 1, 256, 32, 40)])
+def test_attention_simt_mixed_batch(ops, dtype, nq, nkv, d, page, window):
+    """Three requests in one batch: a long prompt portion with earlier context, a single decoded token
+    after hundreds of keys, and a whole short prompt; pages shuffled.  One far key is made to stand out:
+    its score dominates, so losing it (a wrong page, an off-by-one at a page's edge) shows."""
+    rng = np.random.default_rng(7)
+    g = torch.Generator().manual_seed(7)
+    lens, news = [173, 611, 9], [37, 1, 9]
+    scale = d ** -0.5
+    n_pages = sum(-(-L // page) for L in lens) + 4
+    pages = torch.zeros(n_pages, 2, nkv, page, d, dtype=dtype)
+    free = list(rng.permutation(n_pages))
+    qs, refs, tables = [], [], []
+    for L, n in zip(lens, news):
+        k = torch.randn(L, nkv, d, generator=g).to(dtype)
+        v = torch.randn(L, nkv, d, generator=g).to(dtype)
+        q = torch.randn(n, nq, d, generator=g).to(dtype)
+        far = 3 if not window else L - window               # the last query's farthest visible key
+        if L > 100:
+            q[-1, :] = 0
+            q[-1, :, 0] = 6.0
+            k[far, :, 0] = 8.0                              # score 48 * scale: stands out
+            v[far] = 5.0
+            if window:                                      # one key further is out of sight, however loud
+                k[far - 1, :, 0] = 14.0
+                v[far - 1] = -9.0
+        ids = [free.pop() for _ in range(-(-L // page))]
+        for j in range(L):
+            pages[ids[j // page], 0, :, j % page] = k[j]
+            pages[ids[j // page], 1, :, j % page] = v[j]
+        tables.append(ids)
+        qs.append(q)
+        refs.append(reference_attention(q, k, v, scale, window))
+    width = max(len(t) for t in tables)
+    bt = torch.full((3, width), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    q_all = torch.cat(qs).reshape(-1, nq * d)
+    cu = torch.tensor([0, *np.cumsum(news)], dtype=torch.int32)
+    out = torch.empty_like(q_all, device="cuda")
+    ops.attention_simt(out, dev(q_all), dev(pages), dev(bt), dev(cu), dev(torch.tensor(lens, dtype=torch.int32)), 3,
+                       sum(news), nq, nkv, d, scale, window)
+    ref = torch.cat(refs).reshape(-1, nq * d).float()
+    t = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.cpu().float(), ref, **t)
+
+
+@pytest.mark.parametrize("vocab,rows", [(384, 5), (1000, 3), (151936, 4)])
+def test_sampler(ops, vocab, rows):
+    g = torch.Generator().manual_seed(8)
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    temps = torch.tensor([0.0, 0.8, 1.5, 0.3, 1.0][:rows])
+    seeds = torch.tensor([11, 2**40 + 5, 3, 99, 123456789][:rows], dtype=torch.int64)
+    positions = torch.tensor([7, 0, 513, 40, 9][:rows], dtype=torch.int32)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample(out, dev(logits), dev(temps), dev(seeds), dev(positions))
+    got = out.cpu().tolist()
+    for r in range(rows):
+        assert got[r] == plain.sample(logits[r], float(temps[r]), int(seeds[r]), int(positions[r]))
+    # the same request draws the same token whatever else is in the batch
+    out1 = torch.empty(1, dtype=torch.int32, device="cuda")
+    ops.sample(out1, dev(logits[1:2]), dev(temps[1:2]), dev(seeds[1:2]), dev(positions[1:2]))
+    assert out1.item() == got[1]
+
+
+def test_sampler_follows_the_distribution(ops):
+    """Over many seeds the exponential race picks token i with probability softmax(logits / T)_i."""
+    logits = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5, -3.0, 1.5])
+    T, n = 0.7, 20000
+    rows = logits.repeat(n, 1)
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample(out, dev(rows), dev(torch.full((n,), T)), dev(torch.arange(n, dtype=torch.int64) * 7919 + 1),
+               dev(torch.zeros(n, dtype=torch.int32)))
+    freq = torch.bincount(out.cpu().long(), minlength=7).double() / n
+    p = torch.softmax(logits.double() / T, 0)
+    assert (freq - p).abs().max() < 4 * math.sqrt(0.25 / n)

@@ -1,0 +1,78 @@
+"""Trace replay through bin/trace_run against the plain implementation: the same requests
+whole, with the last 32 tokens decoded one by one, in portions of changing size, and mixed
+with other requests in a pool so small that pages are used again; in 32-bit and bfloat16;
+on two tiny configurations."""
+import numpy as np
+import pytest
+import torch
+
+import trace_tools as tt
+from conftest import TINY
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = (40, 71, 90, 33, 57, 64, 1, 9)
+# float32: the engine and the plain implementation add the same numbers in another order.
+# bfloat16: activations are rounded to 8 bits of mantissa after every op; the plain implementation
+# in float32 is the truth, and the error is measured against the spread of the logits.
+F32_TOL = 2e-5
+BF16_REL_TOL = 0.06
+
+
+def requests_for(name):
+    cfg, seed = TINY[name]
+    rng = np.random.default_rng(100 + seed)
+    return {f"r{i}": rng.integers(0, cfg["vocab_size"], n).tolist() for i, n in enumerate(LENGTHS)}
+
+
+@pytest.fixture(scope="module")
+def references(plain_models):
+    return {name: {rid: plain_models[name].logits(t).numpy() for rid, t in requests_for(name).items()}
+            for name in TINY}
+
+
+def check(got, ref, reqs, dtype):
+    for rid, toks in reqs.items():
+        assert sorted(got[rid]) == list(range(len(toks))), f"{rid}: positions missing"
+        g = np.stack([got[rid][p] for p in range(len(toks))])
+        assert np.isfinite(g).all()
+        err = np.abs(g - ref[rid])
+        if dtype == "float32":
+            p = int(err.max(axis=1).argmax())
+            assert err.max() <= F32_TOL, f"{rid}: first bad position {int((err.max(axis=1) > F32_TOL).argmax())}, worst {p}: {err.max():.3e}"
+        else:
+            scale = ref[rid].std()
+            bad = err.max(axis=1) > BF16_REL_TOL * scale
+            assert not bad.any(), f"{rid}: first bad position {int(bad.argmax())}: {err.max() / scale:.3f} of the logits' spread"
+
+
+MODES = {"whole": tt.whole, "decode_tail": tt.decode_tail, "portions": tt.portions, "mixed": tt.mixed}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("name", list(TINY))
+def test_replay_matches_plain(name, mode, dtype, model_dirs, references, tmp_path):
+    cfg, _ = TINY[name]
+    reqs = requests_for(name)
+    steps = MODES[mode](reqs)
+    got = tt.run_trace(model_dirs[name], dtype, steps, str(tmp_path), vocab=cfg["vocab_size"],
+                       page_size=16 if name == "A" else 8)
+    check(got, references[name], reqs, dtype)
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_float32_logits_do_not_depend_on_the_cutting(name, model_dirs, tmp_path):
+    """In 32-bit every kernel fixes the order of its sums per output element, so the logits of a
+    position are the same bits however the tokens were cut and batched and wherever their pages lie."""
+    cfg, _ = TINY[name]
+    reqs = requests_for(name)
+    outs = []
+    for i, mode in enumerate(("whole", "portions", "mixed")):
+        d = tmp_path / mode
+        d.mkdir()
+        outs.append(tt.run_trace(model_dirs[name], "float32", MODES[mode](reqs), str(d), page_size=8 + 8 * (i % 2)))
+    for rid, toks in reqs.items():
+        for p in range(len(toks)):
+            assert np.array_equal(outs[0][rid][p], outs[1][rid][p]) and np.array_equal(outs[0][rid][p], outs[2][rid][p]), \
+                f"{rid} position {p} differs between ways of cutting"
