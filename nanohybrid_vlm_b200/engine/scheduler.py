@@ -59,7 +59,7 @@ class Scheduler:
         if len(seq) >= self.max_model_len:
             raise ValueError(f"prompt of {len(seq)} tokens leaves no room to generate within max_model_len "
                              f"{self.max_model_len}")
-        most = min(len(seq) + seq.max_tokens, self.max_model_len)
+        most = min(len(seq) + seq.max_tokens - 1, self.max_model_len)   # the last token chosen is never fed back
         for g, pool in enumerate(self.cache.pools):
             if -(-most // self.cache.page_size) > pool.num_pages:
                 raise ValueError(f"request of up to {most} tokens can never fit the cache "
