@@ -1,0 +1,295 @@
+"""Benchmark of the engine's decode and prefill steps on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of the Qwen3-8B-shaped configuration (36 layers, width 4096,
+32/8 heads of 128, feed-forward 12288, vocabulary 151936), bfloat16, random weights, batch 8,
+2,048-token uniform-random prompts, decoding inside a 4,096-token context.  A "step" is one decode
+step of the whole batch.  It prints ONE JSON line:
+
+* ``value``: decoded tokens per second, K steps timed on the device with CUDA events;
+* ``e2e``: the same through the Python entry point (``LLM.add_request`` / ``LLM.step``): host
+  token lists in, chosen tokens back on the host every step;
+* ``prefill``: one 2,048-token prompt in one step; ``frac`` = its flops / time / bf16 peak;
+* ``roofline``: bytes the decode step has to read (every weight once, the cache of the live
+  requests) / time, against the HBM peak;
+* ``points``: decode at batch 1 and 64.
+
+Peaks come from MEASURED_PEAKS.json beside this file if present, else the fallback figures
+6.65 TB/s and 1.59 PFLOP/s.  Weights (16 GB) exceed L2 many times over, so every timed step
+reads them from HBM; no L2 flush is needed and ``config.l2`` says so.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIG_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, num_hidden_layers=36,
+                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                 max_position_embeddings=40960, torch_dtype="bfloat16", hidden_act="silu", attention_bias=False)
+FULL_LAYERS = 36
+PROMPT_LEN = 2048
+CONTEXT = 4096
+PAGE = 256
+SEED = 2
+METRIC = "decode tok/s at batch 8 (Qwen3-8B-shaped bf16, 2,048-token prompts, context 4,096)"
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                raw = json.load(f)
+            out["hbm_gbs"] = float(raw.get("hbm_gbs", out["hbm_gbs"]))
+            out["bf16_tflops"] = float(raw.get("bf16_tflops", out["bf16_tflops"]))
+            out["source"] = "measured"
+        except (OSError, ValueError):
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.lines, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def model_numbers(cfg: dict, layers: int) -> dict:
+    H, nq, nkv, d, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                           cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
+    per_layer = (nq + 2 * nkv) * d * H + nq * d * H + 2 * I * H + I * H + 2 * H + 2 * d
+    return {"layer_params": per_layer, "head_params": V * H, "kv_bytes_per_token": 2 * nkv * d * 2 * layers,
+            "weight_bytes": 2 * (layers * per_layer + V * H + H)}
+
+
+def prefill_flops(cfg: dict, layers: int, T: int) -> float:
+    H, nq, d, V = cfg["hidden_size"], cfg["num_attention_heads"], cfg["head_dim"], cfg["vocab_size"]
+    n = model_numbers(cfg, layers)
+    linear = 2.0 * T * (layers * (n["layer_params"] - 2 * H - 2 * d)) + 2.0 * V * H   # one logits row
+    attention = layers * 4.0 * nq * d * (T * (T + 1) / 2)                              # causal QK^T and PV
+    return linear + attention
+
+
+def bench_ours(args) -> dict:
+    import torch
+
+    from nanohybrid_vlm_b200 import LLM, SamplingParams
+    from nanohybrid_vlm_b200.engine import StepItem
+    from nanohybrid_vlm_b200.kernels import library as klib
+
+    layers = args.layers
+    cfg = dict(CONFIG_8B, num_hidden_layers=layers)
+    pk = peaks()
+    nums = model_numbers(cfg, layers)
+    gen = torch.Generator().manual_seed(SEED)
+
+    def prompts(n):
+        return [torch.randint(0, cfg["vocab_size"], (PROMPT_LEN,), generator=gen).tolist() for _ in range(n)]
+
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(cfg, f)
+        max_b = max(args.batch, 64)
+        pages = max_b * (CONTEXT // PAGE) + 2 * (CONTEXT // PAGE)
+        llm = LLM(d, random_weights_seed=SEED, kvcache_block_size=PAGE, num_kvcache_blocks=pages,
+                  max_model_len=CONTEXT, max_num_seqs=max_b, max_num_batched_tokens=8192, seed=SEED)
+    runner = llm.model_runner
+    params = SamplingParams(temperature=0.0, max_tokens=CONTEXT - PROMPT_LEN, ignore_eos=True)
+
+    def device_decode(batch: int, steps: int, warmup: int):
+        """Prefill `batch` prompts, then time `steps` decode steps with CUDA events around the step
+        function and the sampler (device time; the step's metadata copy is part of it)."""
+        ids = [f"d{batch}_{i}" for i in range(batch)]
+        toks = prompts(batch)
+        lens = {}
+        for i, p in zip(ids, toks):          # prefill one request per step (8,192-token budget)
+            runner.cache.allocate(i, PROMPT_LEN + 1)
+            logits = runner.step([StepItem(i, p, 0, [PROMPT_LEN - 1])])
+            lens[i] = PROMPT_LEN
+        last = {i: 1 for i in ids}
+        temps, seeds = [0.0] * batch, list(range(batch))
+
+        def one():
+            items = []
+            for i in ids:
+                runner.cache.allocate(i, lens[i] + 1)
+                items.append(StepItem(i, [last[i]], lens[i], [0]))
+            lg = runner.step(items)
+            chosen = runner.sample(lg, temps, seeds, [lens[i] + 1 for i in ids])
+            for i, t in zip(ids, chosen):
+                last[i] = t
+                lens[i] += 1
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        klib.LAUNCHES = 0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ctx0 = lens[ids[0]]
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        launches = klib.LAUNCHES
+        ctx_mid = ctx0 + steps / 2
+        for i in ids:
+            runner.cache.free(i)
+        return ms, launches, ctx_mid
+
+    def e2e_decode(batch: int, steps: int, warmup: int):
+        """The same through the public API: token lists in, chosen tokens on the host every step."""
+        for p in prompts(batch):
+            llm.add_request(p, params)
+        while llm.scheduler.waiting:
+            llm.step()
+        for _ in range(warmup):
+            llm.step()
+        torch.cuda.synchronize()
+        h0, d0 = llm.h2d_bytes, llm.d2h_bytes
+        t0 = time.perf_counter()
+        n_tok = 0
+        for _ in range(steps):
+            _, stats = llm.step()
+            n_tok += stats.num_decode_tokens
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        h2d, d2h = (llm.h2d_bytes - h0) / steps, (llm.d2h_bytes - d0) / steps
+        for seq in list(llm.scheduler.running):
+            llm.scheduler.cache.free(seq.seq_id)
+        llm.scheduler.running.clear()
+        return n_tok / dt, h2d, d2h
+
+    # prefill of one 2,048-token prompt (3 warm-ups)
+    p = prompts(1)[0]
+    times = []
+    for it in range(5):
+        runner.cache.allocate("pf", PROMPT_LEN)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepItem("pf", p, 0, [PROMPT_LEN - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        runner.cache.free("pf")
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+    pf_ms = sum(times) / len(times)
+    pf_flops = prefill_flops(cfg, layers, PROMPT_LEN)
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms, launches, ctx_mid = device_decode(args.batch, args.steps, args.warmup)
+    clocks = sampler.stop()
+    e2e_tps, h2d, d2h = e2e_decode(args.batch, args.steps, args.warmup)
+    points = {}
+    for b in (1, 64):
+        pms, _, _ = device_decode(b, max(4, args.steps // 2), 3)
+        points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+
+    # every layer's matrices and the head's table once (the embedding is read only at the batch's rows),
+    # plus the keys and values of the live requests at the middle of the timed steps
+    step_bytes = nums["weight_bytes"] + args.batch * ctx_mid * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    value = args.batch / ms * 1e3
+    return {
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random weights N(0,0.02), seed 2)",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B-shaped", "layers": layers, "layers_full": FULL_LAYERS, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE,
+                   "parallelism": "single-gpu", "l2": "inputs_exceed_l2 (16 GB of weights per step, no flush)",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(launches),
+        "prefill": {"value": round(PROMPT_LEN / pf_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
+                    "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+    }
+
+
+def bench_reference(args) -> dict:
+    return {"impl": "reference", "unavailable": "the reference arm is not wired up yet"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+                    help="fewer layers than the full model (sizes of a layer unchanged); recorded in config")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (N=1 only)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    out = bench_reference(args) if args.impl == "reference" else bench_ours(args)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

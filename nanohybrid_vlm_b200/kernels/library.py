@@ -12,6 +12,7 @@ from ctypes import c_float, c_int, c_size_t, c_void_p
 
 _lib = None
 _lock = threading.Lock()
+LAUNCHES = 0    # entry points called since the counter was last reset (each launches at least one kernel)
 
 P, I, F = c_void_p, c_int, c_float
 
@@ -60,6 +61,8 @@ def declare(name: str, argtypes) -> None:
 
 
 def call(name: str, *args) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     lib = library()
     rc = getattr(lib, name)(*args)
     if rc != 0:
