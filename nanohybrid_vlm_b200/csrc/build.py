@@ -142,5 +142,60 @@ def ensure_built(verbose: bool = True) -> str:
     return os.path.join(bdir, LIB_NAME)
 
 
+def ensure_variant(source: str, defines: dict, verbose: bool = True) -> str:
+    """Compile one file of ``csrc/variants/`` with the given -D values into a library of its own
+    (for kernels whose sizes are compile-time constants: a model compiles only what it needs)."""
+    src = os.path.join(CSRC, "variants", source)
+    tag = "_".join(f"{k.lower()}{v}" for k, v in sorted(defines.items()))
+    name = f"libnhv_{os.path.splitext(source)[0]}_{tag}.so"
+    h = hashlib.sha256()
+    for path in (src, os.path.join(CSRC, "nhv_common.cuh")):
+        with open(path, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode() + repr(sorted(defines.items())).encode())
+    digest = h.hexdigest()
+
+    def current(bdir):
+        stamp, lib = os.path.join(bdir, name + ".hash"), os.path.join(bdir, name)
+        if not (os.path.isfile(stamp) and os.path.isfile(lib)):
+            return False
+        with open(stamp) as f:
+            return f.read().strip() == digest
+
+    in_tree = os.path.join(CSRC, "_build")
+    if current(in_tree):
+        return os.path.join(in_tree, name)
+    bdir = build_dir()
+    if current(bdir):
+        return os.path.join(bdir, name)
+    with open(os.path.join(bdir, f".lock_{name}"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if current(bdir):
+            return os.path.join(bdir, name)
+        nvcc = find_nvcc()
+        if verbose:
+            _say(f"compiling {source} for {defines} (first call only)")
+        t0 = time.time()
+        tmp = os.path.join(bdir, f".{name}.{os.getpid()}")
+        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", CSRC, *[f"-D{k}={v}" for k, v in sorted(defines.items())],
+               "-shared", "-o", tmp, src]
+        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        while True:
+            try:
+                out, _ = proc.communicate(timeout=10)
+                break
+            except subprocess.TimeoutExpired:
+                if verbose:
+                    _say(f"  still compiling {source} ({time.time() - t0:.0f} s)")
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {source}:\n{' '.join(cmd)}\n{out}")
+        os.replace(tmp, os.path.join(bdir, name))
+        with open(os.path.join(bdir, name + ".hash"), "w") as f:
+            f.write(digest)
+        if verbose:
+            _say(f"  compiled {source} {defines} in {time.time() - t0:.0f} s")
+    return os.path.join(bdir, name)
+
+
 if __name__ == "__main__":
     print(ensure_built())

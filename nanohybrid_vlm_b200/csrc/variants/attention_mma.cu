@@ -1,0 +1,504 @@
+// bfloat16 attention over cache pages on the tensor cores, compiled once per head size
+// (-DNHV_ATTN_D=<head size>, a multiple of 16 up to 256).
+//
+// Two kernels share one tile routine (64 keys per tile, cp.async double buffering into
+// shared memory, ldmatrix fragments, mma.sync.m16n8k16 bf16 with fp32 accumulation, online
+// softmax in fp32 on base-2 exponents):
+//
+//  * prompt portions (a request brings more than one token): a block owns 64 rows, a row
+//    being (new token, query head of one KV head's group), token-major, so the grouped
+//    query heads share every key/value tile that is read; each of the 4 warps owns 16 rows
+//    and walks all keys up to its rows' positions.
+//  * single decoded tokens: a block owns one (request, KV head, split of 256 keys); the
+//    rows are the group's query heads, all 4 warps hold the same rows and take a quarter
+//    of every 64-key tile each; their partial (max, sum, output) are merged in shared
+//    memory and written to scratch; a second kernel merges the splits in ascending order.
+//
+// Requests with one new token are left to the decode kernel, the others to the prefill
+// kernel, so a mixed batch is two launches plus the merge.  Keys and values of one layer:
+// [page][K|V][kv_head][slot][d] (bf16); a request's logical page p is block_table[p], -1
+// where a window has passed it.  Replaces the library calls at
+// nanovllm/layers/attention.py:67-74.
+#include <math.h>
+
+#include "../nhv_common.cuh"
+
+#ifndef NHV_ATTN_D
+#error "compile with -DNHV_ATTN_D=<head size>"
+#endif
+
+namespace {
+
+constexpr int D = NHV_ATTN_D;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
+constexpr int CH = D / 8;          // 16-byte chunks in a row
+constexpr int ROW_CH = CH + 1;     // padded row stride in chunks: odd, so 8 rows of one chunk column hit 8 bank groups
+constexpr int BN = 64;             // keys per tile
+constexpr int TILE_ELEMS = BN * ROW_CH * 8;
+constexpr int KS = D / 16;         // k-steps of Q.K^T
+constexpr int DN = D / 8;          // n-tiles of P.V
+constexpr int THREADS = 128;
+constexpr int SPLIT = 256;         // keys per decode split
+constexpr float LOG2E = 1.4426950408889634f;
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros and src is not read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// element offset of (row, 16-byte chunk) in a tile
+__device__ __forceinline__ int tile_off(int row, int chunk) { return (row * ROW_CH + chunk) * 8; }
+
+struct PageGeom {
+  const bf16* kv_pages;
+  const int* table;     // this request's block table
+  int nkv, kvh, page_size, n_pages;
+};
+
+// Bring keys [key0, key0 + 64) of one request into a K tile and a V tile; keys outside [lo, hi) or on a
+// page that was given back are zero-filled.
+__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const PageGeom& g, int key0, int lo, int hi) {
+  for (int id = threadIdx.x; id < BN * CH; id += THREADS) {
+    const int r = id / CH, c = id - r * CH;
+    const int j = key0 + r;
+    bool ok = j >= lo && j < hi;
+    const bf16* src = g.kv_pages;
+    if (ok) {
+      const int lp = j / g.page_size;
+      const int page = g.table[lp];
+      ok = page >= 0 && page < g.n_pages;
+      if (ok) src = g.kv_pages + ((((size_t)page * 2) * g.nkv + g.kvh) * g.page_size + (j - lp * g.page_size)) * D + c * 8;
+    }
+    cp_async16(ks + tile_off(r, c), src, ok);
+    cp_async16(vs + tile_off(r, c), ok ? src + (size_t)g.nkv * g.page_size * D : src, ok);
+  }
+}
+
+// Running softmax state of the two rows (lane/4 and lane/4 + 8) a thread holds of its warp's 16 rows.
+struct RowState {
+  float m[2], l[2];
+  float o[DN][4];
+};
+
+// One warp, 16 rows, NT n-tiles of 8 keys starting at tile row `kb`: scores, mask, online softmax, P.V.
+// key_base: absolute index of tile row 0.  Row i (0/1) of this thread sees keys in [row_lo[i], row_hi[i]].
+template <int NT>
+__device__ __forceinline__ void warp_tile(RowState& st, const uint32_t (&qf)[KS][4], const bf16* ks, const bf16* vs,
+                                          int kb, int key_base, const int (&row_lo)[2], const int (&row_hi)[2],
+                                          float scale_log2) {
+  const int lane = threadIdx.x & 31;
+  float s[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+  for (int k = 0; k < KS; ++k) {
+#pragma unroll
+    for (int j = 0; j < NT; j += 2) {
+      uint32_t b[4];
+      // matrices: (keys 8j.., chunk 2k), (keys 8j.., 2k+1), (keys 8(j+1).., 2k), (keys 8(j+1).., 2k+1)
+      ldmatrix_x4(b, ks + tile_off(kb + 8 * j + (lane & 7) + ((lane >> 4) << 3), 2 * k + ((lane >> 3) & 1)));
+      mma_bf16(s[j], qf[k], b[0], b[1]);
+      mma_bf16(s[j + 1], qf[k], b[2], b[3]);
+    }
+  }
+  // mask and the tile's row maxima
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key_base + kb + 8 * j + ((lane & 3) << 1) + (e & 1);
+      const int i = e >> 1;
+      const float v = (key >= row_lo[i] && key <= row_hi[i]) ? s[j][e] * scale_log2 : -INFINITY;
+      s[j][e] = v;
+      mx[i] = fmaxf(mx[i], v);
+    }
+  }
+  float alpha[2], ref[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+    const float m_new = fmaxf(st.m[i], mx[i]);
+    ref[i] = m_new == -INFINITY ? 0.f : m_new;      // a row that has seen no key yet
+    alpha[i] = exp2f(st.m[i] - ref[i]);
+    st.m[i] = m_new;
+    st.l[i] *= alpha[i];
+  }
+#pragma unroll
+  for (int n = 0; n < DN; ++n) {
+    st.o[n][0] *= alpha[0]; st.o[n][1] *= alpha[0];
+    st.o[n][2] *= alpha[1]; st.o[n][3] *= alpha[1];
+  }
+  uint32_t pf[NT / 2][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const float p0 = exp2f(s[j][0] - ref[0]), p1 = exp2f(s[j][1] - ref[0]);
+    const float p2 = exp2f(s[j][2] - ref[1]), p3 = exp2f(s[j][3] - ref[1]);
+    // the sums use the probabilities as rounded for the tensor cores, so numerator and denominator agree
+    const uint32_t lo = pack_bf16(p0, p1), hi = pack_bf16(p2, p3);
+    const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&lo);
+    const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&hi);
+    st.l[0] += __low2float(lo2) + __high2float(lo2);
+    st.l[1] += __low2float(hi2) + __high2float(hi2);
+    pf[j >> 1][(j & 1) * 2 + 0] = lo;
+    pf[j >> 1][(j & 1) * 2 + 1] = hi;
+  }
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+#pragma unroll
+    for (int n = 0; n < DN; n += 2) {
+      uint32_t b[4];
+      // transposed: (keys 16kk.., chunk n), (keys 16kk+8.., chunk n), (keys 16kk.., n+1), (keys 16kk+8.., n+1)
+      ldmatrix_x4_trans(b, vs + tile_off(kb + 16 * kk + (lane & 7) + (((lane >> 3) & 1) << 3), n + (lane >> 4)));
+      mma_bf16(st.o[n], pf[kk], b[0], b[1]);
+      mma_bf16(st.o[n + 1], pf[kk], b[2], b[3]);
+    }
+  }
+}
+
+__device__ __forceinline__ void init_state(RowState& st) {
+  st.m[0] = st.m[1] = -INFINITY;
+  st.l[0] = st.l[1] = 0.f;
+#pragma unroll
+  for (int n = 0; n < DN; ++n) st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.f;
+}
+
+// Load 16 rows of Q fragments for this warp from a staged Q tile (rows row0 .. row0+15).
+__device__ __forceinline__ void load_q_frags(uint32_t (&qf)[KS][4], const bf16* qs, int row0) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int k = 0; k < KS; ++k)
+    ldmatrix_x4(qf[k], qs + tile_off(row0 + (lane & 7) + (((lane >> 3) & 1) << 3), 2 * k + (lane >> 4)));
+}
+
+// ------------------------------------------------------------------------------------------------ prefill
+__global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
+    const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+    const bf16* __restrict__ kv_pages, const int* __restrict__ block_table, int bt_stride,
+    const int* __restrict__ cu_q, const int* __restrict__ kv_len, int n_seqs, int nq, int nkv, int page_size,
+    int n_pages, int window, float scale_log2, int tokens_per_block) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);            // [2][tile]
+  bf16* vbuf = kbuf + 2 * TILE_ELEMS;                        // [2][tile]
+  const int G = nq / nkv;
+  const int kvh = blockIdx.y;
+  int seq = -1, tile = blockIdx.x;
+  for (int s = 0; s < n_seqs; ++s) {
+    const int n = cu_q[s + 1] - cu_q[s];
+    if (n == 1) continue;                                    // single tokens belong to the decode kernel
+    const int nt = (n + tokens_per_block - 1) / tokens_per_block;
+    if (tile < nt) { seq = s; break; }
+    tile -= nt;
+  }
+  if (seq < 0) return;
+  const int n_new = cu_q[seq + 1] - cu_q[seq];
+  const int total = kv_len[seq];
+  const int t0 = tile * tokens_per_block;
+  const int tq_n = min(tokens_per_block, n_new - t0);
+  const int pos0 = total - n_new + t0;                       // position of the block's first token
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // stage Q: row R = token * G + head
+  for (int id = threadIdx.x; id < BN * CH; id += THREADS) {
+    const int R = id / CH, c = id - R * CH;
+    const int tq = R / G, g = R - tq * G;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tq < tq_n)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(cu_q[seq] + t0 + tq) * q_stride + (size_t)(kvh * G + g) * D + c * 8);
+    *reinterpret_cast<uint4*>(kbuf + tile_off(R, c)) = v;
+  }
+  __syncthreads();
+  uint32_t qf[KS][4];
+  load_q_frags(qf, kbuf, warp * 16);
+  __syncthreads();
+
+  int row_lo[2], row_hi[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int R = warp * 16 + (lane >> 2) + 8 * i;
+    const int tq = R / G;
+    if (tq < tq_n) {
+      row_hi[i] = pos0 + tq;
+      row_lo[i] = window > 0 ? max(0, row_hi[i] - window + 1) : 0;
+    } else {
+      row_hi[i] = -1;
+      row_lo[i] = 0;
+    }
+  }
+  const int pos_hi = pos0 + tq_n - 1;
+  const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int key_begin = (first_key / BN) * BN;
+  const int n_tiles = (pos_hi - key_begin) / BN + 1;
+  // this warp's rows: the span of keys any of them sees (warp-uniform, so whole tiles can be skipped)
+  const int w_tq_lo = (warp * 16) / G, w_tq_hi = min((warp * 16 + 15) / G, tq_n - 1);
+  const int w_hi = w_tq_lo < tq_n ? pos0 + w_tq_hi : -1;
+  const int w_lo = window > 0 ? max(0, pos0 + w_tq_lo - window + 1) : 0;
+
+  PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
+  RowState st;
+  init_state(st);
+  load_kv_tile(kbuf, vbuf, geom, key_begin, first_key, pos_hi + 1);
+  cp_async_commit();
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < n_tiles) {
+      load_kv_tile(kbuf + (stage ^ 1) * TILE_ELEMS, vbuf + (stage ^ 1) * TILE_ELEMS, geom, key_begin + (it + 1) * BN,
+                   first_key, pos_hi + 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key_base = key_begin + it * BN;
+    if (key_base <= w_hi && key_base + BN > w_lo)
+      warp_tile<8>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, 0, key_base, row_lo, row_hi, scale_log2);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float l = st.l[i];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int R = warp * 16 + (lane >> 2) + 8 * i;
+    const int tq = R / G, g = R - tq * G;
+    if (tq >= tq_n) continue;
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    bf16* dst = out + (size_t)(cu_q[seq] + t0 + tq) * out_stride + (size_t)(kvh * G + g) * D + ((lane & 3) << 1);
+#pragma unroll
+    for (int n = 0; n < DN; ++n)
+      *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(st.o[n][2 * i] * inv, st.o[n][2 * i + 1] * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ decode
+// scratch per (request, query head, split): D floats of unnormalised output, then (max, sum) in part_ml.
+__global__ void __launch_bounds__(THREADS) attn_decode_split_kernel(
+    const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kv_pages, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len, float* __restrict__ part_o,
+    float* __restrict__ part_ml, int nq, int nkv, int page_size, int n_pages, int window, float scale_log2,
+    int max_splits) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);
+  bf16* vbuf = kbuf + 2 * TILE_ELEMS;
+  const int G = nq / nkv;
+  const int heads_per_block = min(G, 16);
+  const int chunks = (G + 15) / 16;                          // groups of more than 16 heads take several blocks
+  const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y - kvh * chunks) * 16;
+  const int gn = min(heads_per_block, G - g0);
+  const int seq = blockIdx.z, split = blockIdx.x;
+  if (cu_q[seq + 1] - cu_q[seq] != 1) return;
+  const int total = kv_len[seq];
+  const int lo = window > 0 ? max(0, total - window) : 0;
+  const int k0 = max(split * SPLIT, lo), k1 = min(total, (split + 1) * SPLIT);
+  if (k0 >= k1) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t tok = cu_q[seq];
+
+  for (int id = threadIdx.x; id < 16 * CH; id += THREADS) {
+    const int R = id / CH, c = id - R * CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (R < gn) v = *reinterpret_cast<const uint4*>(q + tok * q_stride + (size_t)(kvh * G + g0 + R) * D + c * 8);
+    *reinterpret_cast<uint4*>(kbuf + tile_off(R, c)) = v;
+  }
+  __syncthreads();
+  uint32_t qf[KS][4];
+  load_q_frags(qf, kbuf, 0);
+  __syncthreads();
+
+  int row_lo[2], row_hi[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int R = (lane >> 2) + 8 * i;
+    row_lo[i] = k0;
+    row_hi[i] = R < gn ? k1 - 1 : -1;
+  }
+  const int key_begin = split * SPLIT;
+  const int n_tiles = (k1 - 1 - key_begin) / BN + 1;
+  PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
+  RowState st;
+  init_state(st);
+  load_kv_tile(kbuf, vbuf, geom, key_begin, k0, k1);
+  cp_async_commit();
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < n_tiles) {
+      load_kv_tile(kbuf + (stage ^ 1) * TILE_ELEMS, vbuf + (stage ^ 1) * TILE_ELEMS, geom, key_begin + (it + 1) * BN, k0, k1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key_base = key_begin + it * BN;
+    if (key_base + warp * 16 < k1 && key_base + warp * 16 + 16 > k0)
+      warp_tile<2>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, warp * 16, key_base, row_lo, row_hi, scale_log2);
+    __syncthreads();
+  }
+  // merge the 4 warps (each saw a quarter of every tile) through shared memory
+  float* mo = reinterpret_cast<float*>(smem_raw);            // [4 warps][16 rows][D]
+  float* mml = mo + 4 * 16 * D;                              // [4][16][2]
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float l = st.l[i];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int R = (lane >> 2) + 8 * i;
+    float* dst = mo + ((size_t)warp * 16 + R) * D + ((lane & 3) << 1);
+#pragma unroll
+    for (int n = 0; n < DN; ++n) {
+      dst[n * 8] = st.o[n][2 * i];
+      dst[n * 8 + 1] = st.o[n][2 * i + 1];
+    }
+    if ((lane & 3) == 0) {
+      mml[(warp * 16 + R) * 2] = st.m[i];
+      mml[(warp * 16 + R) * 2 + 1] = l;
+    }
+  }
+  __syncthreads();
+  for (int id = threadIdx.x; id < gn * D; id += THREADS) {
+    const int R = id / D, c = id - R * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + R) * 2]);
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mml[(w * 16 + R) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      acc += mo[((size_t)w * 16 + R) * D + c] * f;
+      L += mml[(w * 16 + R) * 2 + 1] * f;
+    }
+    const size_t slot = ((size_t)seq * nq + kvh * G + g0 + R) * max_splits + split;
+    part_o[slot * D + c] = acc;
+    if (c == 0) {
+      part_ml[slot * 2] = M;
+      part_ml[slot * 2 + 1] = L;
+    }
+  }
+}
+
+// Merge the splits of every (request with one new token, query head), in ascending order of split.
+__global__ void attn_decode_merge_kernel(bf16* __restrict__ out, int out_stride, const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml, const int* __restrict__ cu_q,
+                                         const int* __restrict__ kv_len, int nq, int window, int max_splits) {
+  const int seq = blockIdx.y, head = blockIdx.x;
+  if (cu_q[seq + 1] - cu_q[seq] != 1) return;
+  const int total = kv_len[seq];
+  const int lo = window > 0 ? max(0, total - window) : 0;
+  const int s_first = lo / SPLIT, s_last = (total - 1) / SPLIT;
+  const size_t base = ((size_t)seq * nq + head) * max_splits;
+  float M = -INFINITY;
+  for (int s = s_first; s <= s_last; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  float L = 0.f;
+  for (int s = s_first; s <= s_last; ++s) {
+    const float m = part_ml[(base + s) * 2];
+    L += m == -INFINITY ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(m - M);
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  bf16* dst = out + (size_t)cu_q[seq] * out_stride + (size_t)head * D;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = s_first; s <= s_last; ++s) {
+      const float m = part_ml[(base + s) * 2];
+      if (m != -INFINITY) acc += part_o[(base + s) * D + c] * exp2f(m - M);
+    }
+    dst[c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+constexpr size_t kSmemBytes = (size_t)4 * TILE_ELEMS * sizeof(bf16);
+static_assert(kSmemBytes >= (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float), "merge buffer must fit the tile buffers");
+
+}  // namespace
+
+#define NHV_CAT2(a, b) a##b
+#define NHV_CAT(a, b) NHV_CAT2(a, b)
+#define NHV_FN(name) NHV_CAT(name, NHV_ATTN_D)
+
+static char g_err[384] = "";
+#define ATT_REQUIRE(cond, ...)                      \
+  do {                                              \
+    if (!(cond)) {                                  \
+      snprintf(g_err, sizeof(g_err), __VA_ARGS__);  \
+      return 1;                                     \
+    }                                               \
+  } while (0)
+
+NHV_API const char* NHV_FN(nhv_attn_mma_last_error_d)() { return g_err; }
+NHV_API int NHV_FN(nhv_attn_mma_split_d)() { return SPLIT; }
+
+// The step's attention in bfloat16: prompt portions, then single tokens (split and merge).
+// n_prefill_tokens / n_decode_seqs: how many of the step's tokens / requests are of each kind (0 skips
+// that launch).  scratch_o: [n_seqs * nq * max_splits * D] floats, scratch_ml: [n_seqs * nq * max_splits * 2].
+NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
+                                   const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
+                                   int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
+                                   int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
+                                   float* scratch_ml, int max_splits, cudaStream_t stream) {
+  ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
+  ATT_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
+  ATT_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)kv_pages % 16) == 0,
+              "attention: q and the pages must be 16-byte aligned");
+  const int G = nq / nkv;
+  const float scale_log2 = scale * LOG2E;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) {
+      snprintf(g_err, sizeof(g_err), "attention: cannot reserve %zu bytes of shared memory", kSmemBytes);
+      return 2;
+    }
+    attr_set = true;
+  }
+  if (n_prefill_tokens > 0) {
+    ATT_REQUIRE(G <= BN, "attention: a group of %d query heads is beyond the %d rows of a block", G, BN);
+    const int tokens_per_block = BN / G;
+    const int max_tiles = n_prefill_tokens / tokens_per_block + n_prefill_seqs;
+    dim3 grid(max_tiles, nkv);
+    attn_prefill_kernel<<<grid, THREADS, kSmemBytes, stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
+        n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block);
+  }
+  if (n_decode_seqs > 0) {
+    ATT_REQUIRE(scratch_o && scratch_ml && max_splits > 0, "attention: decoding needs scratch memory for its splits");
+    dim3 grid(max_splits, nkv * ((G + 15) / 16), n_seqs);
+    attn_decode_split_kernel<<<grid, THREADS, kSmemBytes, stream>>>(
+        (const bf16*)q, q_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len, scratch_o, scratch_ml, nq,
+        nkv, page_size, n_pages, window, scale_log2, max_splits);
+    dim3 mgrid(nq, n_seqs);
+    attn_decode_merge_kernel<<<mgrid, D < 128 ? 32 * ((D + 31) / 32) : 128, 0, stream>>>(
+        (bf16*)out, out_stride, scratch_o, scratch_ml, cu_q, kv_len, nq, window, max_splits);
+  }
+  const cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) {
+    snprintf(g_err, sizeof(g_err), "attention: launch failed: %s", cudaGetErrorString(e));
+    return 2;
+  }
+  return 0;
+}

@@ -50,6 +50,9 @@ class StepBatch:
     max_new_tokens: int = 0
     max_kv_len: int = 0
     decode_only: bool = False
+    n_decode_seqs: int = 0          # requests that bring exactly one token
+    n_prefill_seqs: int = 0         # requests that bring more
+    n_prefill_tokens: int = 0
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -158,4 +161,6 @@ class BatchBuilder:
             cu_q=dev("cu_q"), kv_len=dev("kv_len"), q_start=dev("q_start"), state_slots=dev("state_slots"),
             logit_rows=dev("logit_rows"), groups=groups, host_cu_q=[int(x) for x in cu[:S + 1]],
             host_kv_len=[it.start + n for it, n in zip(items, lens)], max_new_tokens=max(lens),
-            max_kv_len=max(it.start + n for it, n in zip(items, lens)), decode_only=max(lens) == 1)
+            max_kv_len=max(it.start + n for it, n in zip(items, lens)), decode_only=max(lens) == 1,
+            n_decode_seqs=sum(1 for n in lens if n == 1), n_prefill_seqs=sum(1 for n in lens if n > 1),
+            n_prefill_tokens=sum(n for n in lens if n > 1))

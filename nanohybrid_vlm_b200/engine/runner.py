@@ -12,7 +12,7 @@ import torch
 
 from ..cache import CacheLayout, CacheManager, CacheStorage
 from ..config import Config
-from ..kernels import library, ops
+from ..kernels import load_library, ops
 from ..weights import load_weights, materialize_random
 from .batch import BatchBuilder, StepItem
 from .model import CausalLM
@@ -22,7 +22,7 @@ class ModelRunner:
     def __init__(self, config: Config, *, random_weights_seed: int | None = None, device: str = "cuda:0"):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this engine computes on a B200 only and has no CPU fallback")
-        library()   # compile / load the kernels now; fail loudly if that is impossible
+        load_library()   # compile / load the kernels now; fail loudly if that is impossible
         self.config = config
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)

@@ -1,4 +1,5 @@
-from .library import KernelError, library
+from . import library
+from .library import KernelError, load_library
 from . import ops
 
-__all__ = ["KernelError", "library", "ops"]
+__all__ = ["KernelError", "library", "load_library", "ops"]

@@ -33,7 +33,7 @@ class KernelError(RuntimeError):
     pass
 
 
-def library() -> ctypes.CDLL:
+def load_library() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         with _lock:
@@ -63,7 +63,7 @@ def declare(name: str, argtypes) -> None:
 def call(name: str, *args) -> None:
     global LAUNCHES
     LAUNCHES += 1
-    lib = library()
+    lib = load_library()
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(lib.nhv_last_error().decode(errors="replace"))

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import torch
 
+from . import attention_mma, library
 from .library import KernelError, call
 
 F32, BF16 = 0, 1
@@ -125,9 +126,42 @@ def attention_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_t
 
 
 def attention(out, q, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int, scale: float, window: int = 0) -> None:
-    """Attention of the step's tokens over the cache: picks the kernel for the dtype and sizes."""
-    attention_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
-                   nq, nkv, head_dim, scale, window)
+    """Attention of the step's tokens over the cache: picks the kernel for the dtype and sizes.
+    bfloat16 with a head size in steps of 16 runs on the tensor cores; everything else (float32, other
+    head sizes, groups of more than 64 heads) on the CUDA cores."""
+    if q.dtype == torch.bfloat16 and attention_mma.supports(head_dim, nq, nkv):
+        attention_tensor_core(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs,
+                              batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len,
+                              nq, nkv, head_dim, scale, window)
+    else:
+        attention_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
+                       nq, nkv, head_dim, scale, window)
+
+
+def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_prefill_tokens: int,
+                          n_prefill_seqs: int, n_decode_seqs: int, max_kv_len: int, nq: int, nkv: int, head_dim: int,
+                          scale: float, window: int = 0) -> None:
+    """bfloat16 attention on the tensor cores.  Requests with one new token go through the split
+    kernel and its merge (scratch: one partial result per request, head and split of 256 keys); the
+    others through the prompt kernel."""
+    _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len)
+    _contig("kv_pages", kv_pages)
+    assert q.dtype == out.dtype == kv_pages.dtype == torch.bfloat16 and q.stride(-1) == 1 and out.stride(-1) == 1
+    n_pages, two, h, page_size, d = kv_pages.shape
+    assert two == 2 and h == nkv and d == head_dim
+    assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
+    launch, split = attention_mma.get(head_dim)
+    scratch_o = scratch_ml = None
+    max_splits = 0
+    if n_decode_seqs > 0:
+        max_splits = -(-max_kv_len // split)
+        scratch_o = torch.empty(n_seqs * nq * max_splits * head_dim, dtype=torch.float32, device=q.device)
+        scratch_ml = torch.empty(n_seqs * nq * max_splits * 2, dtype=torch.float32, device=q.device)
+    library.LAUNCHES += 1
+    launch(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
+           block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
+           n_decode_seqs, nq, nkv, page_size, n_pages, int(window), float(scale), _ptr(scratch_o), _ptr(scratch_ml),
+           max_splits, stream_ptr())
 
 
 def linear(out, x, weight) -> None:

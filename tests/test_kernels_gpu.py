@@ -187,20 +187,25 @@ def reference_attention(q, k, v, scale, window):
     return out
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 16, 0), (6, 2, 32, 8, 0), (3, 3, 48, 1, 0),
-                                                  (14, 2, 80, 5, 0), (8, 1, 128, 64, 0), (18, 2, 64, 16, 0),
-                                                  (4, 2, 32, 8, 19), (2, 1, 256, 32, 40)])
-def test_attention_simt_mixed_batch(ops, dtype, nq, nkv, d, page, window):
-    """Three requests in one batch: a long prompt portion with earlier context, a single decoded token
-    after hundreds of keys, and a whole short prompt; pages shuffled.  One far key is made to stand out:
-    its score dominates, so losing it (a wrong page, an off-by-one at a page's edge) shows."""
+ATTENTION_SHAPES = [(4, 2, 16, 16, 0), (6, 2, 32, 8, 0), (3, 3, 48, 1, 0), (14, 2, 80, 5, 0), (8, 1, 128, 64, 0),
+                    (18, 2, 64, 16, 0), (4, 2, 32, 8, 19), (2, 1, 256, 32, 40), (32, 8, 128, 256, 0),
+                    (34, 1, 64, 16, 300)]
+
+
+@pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
+                                          ("tensor_core", torch.bfloat16)])
+@pytest.mark.parametrize("nq,nkv,d,page,window", ATTENTION_SHAPES)
+def test_attention_mixed_batch(ops, kernel, dtype, nq, nkv, d, page, window):
+    """Five requests in one batch: a long prompt portion with earlier context, a single decoded token
+    after hundreds of keys, a whole short prompt, a decoded token with few keys and a two-token portion;
+    pages shuffled and the pool poisoned with NaN.  One far key is made to stand out: its score
+    dominates, so losing it (a wrong page, an off-by-one at a page's edge or a split's edge) shows."""
     rng = np.random.default_rng(7)
     g = torch.Generator().manual_seed(7)
-    lens, news = [173, 611, 9], [37, 1, 9]
+    lens, news = [173, 611, 9, 5, 258], [37, 1, 9, 1, 2]
     scale = d ** -0.5
     n_pages = sum(-(-L // page) for L in lens) + 4
-    pages = torch.zeros(n_pages, 2, nkv, page, d, dtype=dtype)
+    pages = torch.full((n_pages, 2, nkv, page, d), float("nan")).to(dtype)
     free = list(rng.permutation(n_pages))
     qs, refs, tables = [], [], []
     for L, n in zip(lens, news):
@@ -224,14 +229,20 @@ def test_attention_simt_mixed_batch(ops, dtype, nq, nkv, d, page, window):
         qs.append(q)
         refs.append(reference_attention(q, k, v, scale, window))
     width = max(len(t) for t in tables)
-    bt = torch.full((3, width), -1, dtype=torch.int32)
+    S = len(lens)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
     for i, t in enumerate(tables):
         bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
     q_all = torch.cat(qs).reshape(-1, nq * d)
     cu = torch.tensor([0, *np.cumsum(news)], dtype=torch.int32)
-    out = torch.empty_like(q_all, device="cuda")
-    ops.attention_simt(out, dev(q_all), dev(pages), dev(bt), dev(cu), dev(torch.tensor(lens, dtype=torch.int32)), 3,
-                       sum(news), nq, nkv, d, scale, window)
+    out = torch.full_like(q_all, float("nan"), device="cuda")
+    kv = dev(torch.tensor(lens, dtype=torch.int32))
+    if kernel == "simt":
+        ops.attention_simt(out, dev(q_all), dev(pages), dev(bt), dev(cu), kv, S, sum(news), nq, nkv, d, scale, window)
+    else:
+        ops.attention_tensor_core(out, dev(q_all), dev(pages), dev(bt), dev(cu), kv, S,
+                                  sum(n for n in news if n > 1), sum(1 for n in news if n > 1),
+                                  sum(1 for n in news if n == 1), max(lens), nq, nkv, d, scale, window)
     ref = torch.cat(refs).reshape(-1, nq * d).float()
     t = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(out.cpu().float(), ref, **t)
