@@ -148,8 +148,9 @@ def bench_ours(args) -> dict:
     params = SamplingParams(temperature=0.0, max_tokens=CONTEXT - PROMPT_LEN, ignore_eos=True)
 
     def device_decode(batch: int, steps: int, warmup: int):
-        """Prefill `batch` prompts, then time `steps` decode steps with CUDA events around the step
-        function and the sampler (device time; the step's metadata copy is part of it)."""
+        """Prefill `batch` prompts, then time `steps` decode steps with CUDA events around the runner's
+        step-and-sample call (the captured graph of the step, its metadata copy before, the read of the
+        chosen tokens after)."""
         ids = [f"d{batch}_{i}" for i in range(batch)]
         toks = prompts(batch)
         lens = {}
@@ -158,15 +159,13 @@ def bench_ours(args) -> dict:
             logits = runner.step([StepItem(i, p, 0, [PROMPT_LEN - 1])])
             lens[i] = PROMPT_LEN
         last = {i: 1 for i in ids}
-        temps, seeds = [0.0] * batch, list(range(batch))
 
         def one():
             items = []
             for i in ids:
                 runner.cache.allocate(i, lens[i] + 1)
                 items.append(StepItem(i, [last[i]], lens[i], [0]))
-            lg = runner.step(items)
-            chosen = runner.sample(lg, temps, seeds, [lens[i] + 1 for i in ids])
+            chosen = runner.run(items, [(0.0, n, lens[i] + 1) for n, i in enumerate(ids)])
             for i, t in zip(ids, chosen):
                 last[i] = t
                 lens[i] += 1

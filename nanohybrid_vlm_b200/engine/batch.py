@@ -53,6 +53,10 @@ class StepBatch:
     n_decode_seqs: int = 0          # requests that bring exactly one token
     n_prefill_seqs: int = 0         # requests that bring more
     n_prefill_tokens: int = 0
+    # sampling inputs, one per wanted row (None if the caller only wants logits)
+    temperatures: torch.Tensor | None = None    # [R] float32
+    seeds: torch.Tensor | None = None           # [R] int64
+    sample_positions: torch.Tensor | None = None  # [R] int32: the position of the token being chosen
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -77,7 +81,8 @@ class BatchBuilder:
 
     def _layout(self, T: int, S: int, R: int, width: int):
         off, sections = 0, {}
-        for name, n in (("token_ids", T), ("positions", T), ("cu_q", S + 1), ("kv_len", S), ("q_start", S),
+        for name, n in (("seeds", 2 * R), ("temperatures", R), ("sample_positions", R), ("token_ids", T),
+                        ("positions", T), ("cu_q", S + 1), ("kv_len", S), ("q_start", S),
                         ("state_slots", S), ("logit_rows", R)):
             sections[name] = (off, n)
             off += _align(n)
@@ -88,16 +93,24 @@ class BatchBuilder:
             off += _align(S * width)
         return sections, off
 
-    def build(self, items: list[StepItem], table_width: int | None = None) -> StepBatch:
-        S = len(items)
-        T = sum(len(it.tokens) for it in items)
-        R = sum(len(it.want) for it in items)
+    def build(self, items: list[StepItem], table_width: int | None = None, sampling=None,
+              pad_to: int | None = None) -> StepBatch:
+        """``sampling``: one (temperature, seed, position of the token being chosen) per wanted row.
+        ``pad_to``: for a batch of single tokens, fill up to this many requests with idle entries (one
+        token that is stored nowhere and reads no page), so that the batch has a fixed shape."""
+        n_real = len(items)
+        pad = 0 if pad_to is None else pad_to - n_real
+        if pad < 0 or (pad_to is not None and any(len(it.tokens) != 1 or it.want != [0] for it in items)):
+            raise ValueError("only a batch of single tokens that all want their logits can be padded")
+        S = n_real + pad
+        T = sum(len(it.tokens) for it in items) + pad
+        R = sum(len(it.want) for it in items) + pad
         if S == 0 or T == 0:
             raise ValueError("a step needs at least one request with at least one token")
         if S > self.max_seqs or T > self.max_tokens:
             raise ValueError(f"step of {S} requests / {T} tokens is beyond the limits {self.max_seqs} / {self.max_tokens}")
         ps = self.page_size
-        width = table_width or max(1, max(-(-(it.start + len(it.tokens)) // ps) for it in items))
+        width = table_width or max(1, max((-(-(it.start + len(it.tokens)) // ps) for it in items), default=1))
         if width > self.max_pages:
             raise ValueError(f"a request needs {width} pages, beyond the limit of {self.max_pages}")
         sec, total = self._layout(T, S, R, width)
@@ -115,6 +128,15 @@ class BatchBuilder:
         table_views = [view(f"tables{g}").reshape(S, width) for g in range(self.n_groups)]
         for tv in table_views:
             tv.fill(-1)
+        if sampling is not None:
+            if len(sampling) != R - pad:
+                raise ValueError("one (temperature, seed, position) per wanted row is needed")
+            temps = view("temperatures").view(np.float32)
+            seeds = view("seeds").view(np.int64)
+            spos = view("sample_positions")
+            temps[:], seeds[:], spos[:] = 0.0, 0, 0
+            for i, (temp, seed, p) in enumerate(sampling):
+                temps[i], seeds[i], spos[i] = temp, seed, p
         t = r = 0
         cu[0] = 0
         for s, it in enumerate(items):
@@ -143,6 +165,15 @@ class BatchBuilder:
                 pages = table[p // ps]
                 slot_views[g][t:t + n] = np.where(pages >= 0, pages * ps + p % ps, -1)
             t += n
+        for s in range(n_real, S):          # idle entries
+            tok[t], pos[t] = 0, 0
+            cu[s + 1] = t + 1
+            kvl[s], qs[s], st[s] = 1, 0, -1
+            rows[r] = t
+            for g in range(self.n_groups):
+                slot_views[g][t] = -1
+            t += 1
+            r += 1
         if tok[:T].min() < 0 or tok[:T].max() >= self.vocab:
             raise ValueError(f"token ids must lie in [0, {self.vocab})")
         self._dev[:total].copy_(self._host[:total], non_blocking=True)
@@ -155,12 +186,17 @@ class BatchBuilder:
             return self._dev[o:o + n]
 
         groups = [GroupTables(dev(f"tables{g}").view(S, width), dev(f"slots{g}")) for g in range(self.n_groups)]
-        lens = [len(it.tokens) for it in items]
-        return StepBatch(
+        lens = [len(it.tokens) for it in items] + [1] * pad
+        ends = [it.start + len(it.tokens) for it in items] + [1] * pad
+        samp = {}
+        if sampling is not None:
+            samp = dict(temperatures=dev("temperatures").view(torch.float32), seeds=dev("seeds").view(torch.int64),
+                        sample_positions=dev("sample_positions"))
+        return StepBatch(**samp,
             n_tokens=T, n_seqs=S, n_logit_rows=R, token_ids=dev("token_ids"), positions=dev("positions"),
             cu_q=dev("cu_q"), kv_len=dev("kv_len"), q_start=dev("q_start"), state_slots=dev("state_slots"),
             logit_rows=dev("logit_rows"), groups=groups, host_cu_q=[int(x) for x in cu[:S + 1]],
-            host_kv_len=[it.start + n for it, n in zip(items, lens)], max_new_tokens=max(lens),
-            max_kv_len=max(it.start + n for it, n in zip(items, lens)), decode_only=max(lens) == 1,
+            host_kv_len=ends, max_new_tokens=max(lens),
+            max_kv_len=max(ends) if pad_to is None else width * ps, decode_only=max(lens) == 1,
             n_decode_seqs=sum(1 for n in lens if n == 1), n_prefill_seqs=sum(1 for n in lens if n > 1),
             n_prefill_tokens=sum(n for n in lens if n > 1))

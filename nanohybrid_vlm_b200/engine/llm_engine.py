@@ -148,15 +148,14 @@ class LLMEngine:
             if m.first_scheduled_time is None:
                 m.first_scheduled_time = t0
         runner = self.model_runner
-        logits = runner.step(items)
-        self.h2d_bytes += runner.builder.bytes_last_copy
         tokens = {}
         if sampled:
-            chosen = runner.sample(logits, [s.temperature for s in sampled], [s.seed for s in sampled],
-                                   [len(s) for s in sampled])
-            self.h2d_bytes += 16 * len(sampled)
+            chosen = runner.run(items, [(s.temperature, s.seed, len(s)) for s in sampled])
             self.d2h_bytes += 4 * len(sampled)
             tokens = {s.seq_id: t for s, t in zip(sampled, chosen)}
+        else:
+            runner.step(items)
+        self.h2d_bytes += runner.builder.bytes_last_copy
         self.scheduler.postprocess(plan.seqs, [tokens.get(s.seq_id) for s in plan.seqs])
         now = perf_counter()
         outputs = []

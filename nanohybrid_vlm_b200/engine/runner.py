@@ -12,7 +12,7 @@ import torch
 
 from ..cache import CacheLayout, CacheManager, CacheStorage
 from ..config import Config
-from ..kernels import load_library, ops
+from ..kernels import library, load_library, ops
 from ..weights import load_weights, materialize_random
 from .batch import BatchBuilder, StepItem
 from .model import CausalLM
@@ -49,7 +49,12 @@ class ModelRunner:
         self.builder = BatchBuilder(self.cache, self.vocab_size, self.device,
                                     max_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,
                                     max_pages_per_seq=self.max_pages_per_seq)
-        self.kernel_launches = 0
+        # CUDA graphs of the decode step, one per batch-size bucket, captured at first use
+        # (the reference captures the same buckets up front, nanovllm/engine/model_runner.py:2560-2594)
+        self.graph_buckets = [] if config.enforce_eager else [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+                                                             if b <= config.max_num_seqs]
+        self._graphs: dict[int, tuple] = {}
+        self._graph_pool = None
 
     # ------------------------------------------------------------------ sizing
     def _activation_allowance(self) -> int:
@@ -87,6 +92,58 @@ class ModelRunner:
         in the order of the items and of each item's ``want``."""
         batch = self.builder.build(items)
         return self.model.forward(batch, self.storage)
+
+    @torch.no_grad()
+    def run(self, items: list[StepItem], sampling) -> list[int]:
+        """The step followed by the choice of one token per wanted row; host lists in, host list out.
+        ``sampling``: (temperature, seed, position of the token being chosen) per wanted row.  A batch
+        of single tokens replays the captured graph of its size bucket; anything else runs eagerly."""
+        bucket = self._bucket(items)
+        if bucket is None:
+            batch = self.builder.build(items, sampling=sampling)
+            logits = self.model.forward(batch, self.storage)
+            out = torch.empty(batch.n_logit_rows, dtype=torch.int32, device=self.device)
+            ops.sample(out, logits, batch.temperatures, batch.seeds, batch.sample_positions)
+            return out.tolist()
+        if bucket not in self._graphs:
+            self._capture(bucket)
+        graph, tokens, launches = self._graphs[bucket]
+        self.builder.build(items, table_width=self.max_pages_per_seq, sampling=sampling, pad_to=bucket)
+        graph.replay()
+        library.LAUNCHES += launches     # the kernels that the replay launched
+        return tokens[:len(items)].tolist()
+
+    def _bucket(self, items) -> int | None:
+        if not self.graph_buckets or len(items) > self.graph_buckets[-1]:
+            return None
+        if any(len(it.tokens) != 1 or it.want != [0] for it in items):
+            return None
+        return next(b for b in self.graph_buckets if b >= len(items))
+
+    def _capture(self, bucket: int) -> None:
+        """Capture model + sampler for `bucket` single-token requests.  The batch's device arrays live at
+        fixed places of the builder's buffer for a given shape, so a replay reads what the next
+        ``build`` of the same shape copied there."""
+        def one_step():
+            batch = self.builder.build([], table_width=self.max_pages_per_seq, sampling=[], pad_to=bucket)
+            logits = self.model.forward(batch, self.storage)
+            out = torch.empty(bucket, dtype=torch.int32, device=self.device)
+            ops.sample(out, logits, batch.temperatures, batch.seeds, batch.sample_positions)
+            return out
+
+        one_step()                       # warm up: library workspaces and kernel attributes are set outside capture
+        torch.cuda.synchronize()
+        batch = self.builder.build([], table_width=self.max_pages_per_seq, sampling=[], pad_to=bucket)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        launches_before = library.LAUNCHES
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(batch, self.storage)
+            tokens = torch.empty(bucket, dtype=torch.int32, device=self.device)
+            ops.sample(tokens, logits, batch.temperatures, batch.seeds, batch.sample_positions)
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        self._graphs[bucket] = (graph, tokens, library.LAUNCHES - launches_before)
 
     @torch.no_grad()
     def sample(self, logits: torch.Tensor, temperatures, seeds, positions) -> list[int]:

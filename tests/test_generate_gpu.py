@@ -1,0 +1,137 @@
+"""Generation through the Python entry point against the plain implementation: greedy tokens, long
+decoding, the first tokens of a sequence, prompts cut into portions beside decoding requests, a pool
+so small that requests are preempted and recomputed, seeded temperature sampling."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+def make_llm(model_dir, name, dtype="float32", **kw):
+    from nanohybrid_vlm_b200 import LLM
+    opts = dict(dtype=dtype, kvcache_block_size=16 if name == "A" else 8, num_kvcache_blocks=128, max_num_seqs=8,
+                max_num_batched_tokens=64, max_model_len=TINY[name][0]["max_position_embeddings"])
+    opts.update(kw)
+    return LLM(model_dir, **opts)
+
+
+def prompts_for(name, lengths, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, TINY[name][0]["vocab_size"], n).tolist() for n in lengths]
+
+
+def assert_greedy_follows(plain_model, prompt, tokens, slack):
+    """Each generated token is the plain implementation's best token for the same prefix, or within
+    `slack` of it (two logits that close may swap under bfloat16)."""
+    seq = list(prompt)
+    for t in tokens:
+        lg = plain_model.logits(seq)[-1]
+        assert lg[t] >= lg.max() - slack, f"token {t} at position {len(seq)}: logit {lg[t]:.4f} vs best {lg.max():.4f}"
+        seq.append(t)
+
+
+@pytest.mark.parametrize("name,lengths,new", [("A", (5, 17, 33), 8), ("B", (1, 9, 40, 71), 12)])
+def test_greedy_matches_plain_in_float32(name, lengths, new, model_dirs, plain_models):
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompts = prompts_for(name, lengths)
+    want = [plain_models[name].greedy(p, new) for p in prompts]
+    for eager in (True, False):
+        llm = make_llm(model_dirs[name], name, enforce_eager=eager)
+        out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True), use_tqdm=False)
+        assert [o["token_ids"] for o in out] == want, f"enforce_eager={eager}"
+        assert all(o["text"] == "" for o in out)
+        llm.model_runner.cache.check()
+        assert llm.model_runner.cache.num_live() == 0
+        del llm
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_greedy_in_bfloat16_follows_plain(name, model_dirs, plain_models):
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompts = prompts_for(name, (3, 20, 45), seed=1)
+    llm = make_llm(model_dirs[name], name, dtype="bfloat16")
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True), use_tqdm=False)
+    for p, o in zip(prompts, out):
+        assert len(o["token_ids"]) == 10
+        assert_greedy_follows(plain_models[name], p, o["token_ids"], slack=0.03)
+
+
+def test_long_decoding_and_first_tokens(model_dirs, plain_models):
+    """One- and two-token prompts decoded for 150 tokens: every page edge of a short context is crossed
+    token by token, through captured graphs."""
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompts = prompts_for("A", (1, 2, 3), seed=2)
+    llm = make_llm(model_dirs["A"], "A")
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=150, ignore_eos=True), use_tqdm=False)
+    for p, o in zip(prompts, out):
+        assert o["token_ids"] == plain_models["A"].greedy(p, 150)
+
+
+def test_portions_beside_decoding_and_preemption_leave_tokens_unchanged(model_dirs, plain_models):
+    """Tiny B's workload: prompts of 1, 9, 40 and 71 tokens prefilled in portions of 13 mixed with
+    decoding requests; then the same with so few pages that requests are preempted and recomputed."""
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompts = prompts_for("B", (1, 9, 40, 71), seed=3)
+    want = [plain_models["B"].greedy(p, 12) for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    llm = make_llm(model_dirs["B"], "B", max_portion=13)
+    assert [o["token_ids"] for o in llm.generate(prompts, sp, use_tqdm=False)] == want
+    del llm
+    # 71 + 11 tokens need 11 pages of 8; with 14 pages the four requests cannot all stay resident
+    llm = make_llm(model_dirs["B"], "B", num_kvcache_blocks=14, max_portion=13)
+    assert [o["token_ids"] for o in llm.generate(prompts, sp, use_tqdm=False)] == want
+    assert llm.scheduler.num_preemptions > 0
+    llm.model_runner.cache.check()
+    assert all(p.num_free == p.num_pages for p in llm.model_runner.cache.pools)
+
+
+def test_eos_stops_a_request(model_dirs, plain_models):
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompt = prompts_for("B", (12,), seed=4)[0]
+    ref = plain_models["B"].greedy(prompt, 12)
+    llm = make_llm(model_dirs["B"], "B", eos=ref[4])
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=12), use_tqdm=False)[0]["token_ids"]
+    stop = ref.index(ref[4])
+    assert out == ref[:stop + 1]
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_the_batch(model_dirs, plain_models):
+    """Temperature 0.8 with per-request seeds: a request draws the same tokens alone, in a batch, with
+    its prompt cut into portions, and they are the tokens the plain sampler draws from the plain
+    implementation's logits."""
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompts = prompts_for("B", (1, 9, 40, 71), seed=5)
+    sps = [SamplingParams(temperature=0.8, max_tokens=12, ignore_eos=True, seed=100 + i) for i in range(4)]
+    llm = make_llm(model_dirs["B"], "B", max_portion=13)
+    together = [o["token_ids"] for o in llm.generate(prompts, sps, use_tqdm=False)]
+    alone = [llm.generate([p], sp, use_tqdm=False)[0]["token_ids"] for p, sp in zip(prompts, sps)]
+    assert together == alone
+    other = llm.generate([prompts[2]], SamplingParams(temperature=0.8, max_tokens=12, ignore_eos=True, seed=7),
+                         use_tqdm=False)[0]["token_ids"]
+    assert other != together[2]
+    for p, sp, got in zip(prompts, sps, together):
+        seq = list(p)
+        for t in got:
+            lg = plain_models["B"].logits(seq)[-1]
+            assert t == plain.sample(lg, 0.8, sp.seed, len(seq))
+            seq.append(t)
+
+
+def test_entry_point_checks_its_input(model_dirs):
+    from nanohybrid_vlm_b200 import SamplingParams
+    llm = make_llm(model_dirs["A"], "A")
+    sp = SamplingParams(temperature=0.0, max_tokens=2)
+    for bad, exc in (([], ValueError), ([1, -2], ValueError), ([1, True], TypeError), ((1, 2), TypeError),
+                     ([1, 256], ValueError), ("text", ValueError)):
+        with pytest.raises(exc):
+            llm.add_request(bad, sp)
+    with pytest.raises(TypeError, match="unknown engine options"):
+        make_llm(model_dirs["A"], "A", no_such_option=1)
+    with pytest.raises(ValueError):
+        SamplingParams(temperature=-1.0)
+    with pytest.raises(ValueError):
+        SamplingParams(temperature=float("nan"))
