@@ -143,7 +143,8 @@ def bench_ours(args) -> dict:
         max_b = max(args.batch, 64)
         pages = max_b * (CONTEXT // PAGE) + 2 * (CONTEXT // PAGE)
         llm = LLM(d, random_weights_seed=SEED, kvcache_block_size=PAGE, num_kvcache_blocks=pages,
-                  max_model_len=CONTEXT, max_num_seqs=max_b, max_num_batched_tokens=8192, seed=SEED)
+                  max_model_len=CONTEXT, max_num_seqs=max_b, max_num_batched_tokens=8192, seed=SEED,
+                  enforce_eager=args.eager)
     runner = llm.model_runner
     params = SamplingParams(temperature=0.0, max_tokens=CONTEXT - PROMPT_LEN, ignore_eos=True)
 
@@ -211,6 +212,10 @@ def bench_ours(args) -> dict:
         llm.scheduler.running.clear()
         return n_tok / dt, h2d, d2h
 
+    if args.only == "decode":
+        ms, launches, _ = device_decode(args.batch, args.steps, args.warmup)
+        print(f"decode batch {args.batch}: {ms:.3f} ms/step, {launches} launches")
+        return None
     # prefill of one 2,048-token prompt (3 warm-ups)
     p = prompts(1)[0]
     times = []
@@ -226,6 +231,9 @@ def bench_ours(args) -> dict:
         if it >= 3:
             times.append(e0.elapsed_time(e1))
     pf_ms = sum(times) / len(times)
+    if args.only == "prefill":
+        print(f"prefill {PROMPT_LEN} tokens: {pf_ms:.3f} ms")
+        return None
     pf_flops = prefill_flops(cfg, layers, PROMPT_LEN)
 
     sampler = ClockSampler()
@@ -277,6 +285,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for per-kernel profiling)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run only the decode steps or only the prefill step (profiling); prints no JSON line")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS,
                     help="fewer layers than the full model (sizes of a layer unchanged); recorded in config")
     args = ap.parse_args()
@@ -286,7 +297,8 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
     out = bench_reference(args) if args.impl == "reference" else bench_ours(args)
-    print(json.dumps(out))
+    if out is not None:
+        print(json.dumps(out))
     return 0
 
 

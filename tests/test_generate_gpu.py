@@ -81,8 +81,9 @@ def test_portions_beside_decoding_and_preemption_leave_tokens_unchanged(model_di
     llm = make_llm(model_dirs["B"], "B", max_portion=13)
     assert [o["token_ids"] for o in llm.generate(prompts, sp, use_tqdm=False)] == want
     del llm
-    # 71 + 11 tokens need 11 pages of 8; with 14 pages the four requests cannot all stay resident
-    llm = make_llm(model_dirs["B"], "B", num_kvcache_blocks=14, max_portion=13)
+    # the prompts take 1 + 2 + 5 + 9 = 17 pages of 8 tokens, so all four are admitted into 19 pages; twelve
+    # tokens later they would hold 23, so decoding runs out of pages on the way
+    llm = make_llm(model_dirs["B"], "B", num_kvcache_blocks=19, max_portion=13)
     assert [o["token_ids"] for o in llm.generate(prompts, sp, use_tqdm=False)] == want
     assert llm.scheduler.num_preemptions > 0
     llm.model_runner.cache.check()
