@@ -1,0 +1,305 @@
+"""Each part of a layer alone against the plain implementation's function for it, and a toy
+architecture, defined here, whose layers mix a mixer with fixed-size state of its own with attention,
+run one layer twice and let a run read another run's cache: registered, built from random weights and
+stepped without a change to the framework's files."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def build_part(registry, spec, hidden, dtype=torch.float32, max_position=256, seed=0):
+    from nanohybrid_vlm_b200.parts import BuildEnv
+    env = BuildEnv(hidden, dtype, "cuda", max_position)
+    obj = registry.get(spec.kind)(spec, env)
+    g = torch.Generator().manual_seed(seed)
+    host = {}
+    for decl in obj.params():
+        t = torch.randn(decl.shape, generator=g) * 0.05
+        if decl.init == "norm":
+            t = 1 + t
+        host[decl.name] = t.to(dtype)
+    obj.bind({k: v.cuda() for k, v in host.items()})
+    return obj, host
+
+
+class OneRequest:
+    """A cache and batch builder for parts tested alone: one group of pages, requests by name."""
+
+    def __init__(self, need, page_size=8, num_pages=64, dtype=torch.float32, vocab=1000):
+        from nanohybrid_vlm_b200.cache import CacheLayout, CacheManager, CacheStorage
+        from nanohybrid_vlm_b200.engine.batch import BatchBuilder
+        from nanohybrid_vlm_b200.parts import LayerRun
+        self.layout = CacheLayout.from_needs([need])
+        self.cm = CacheManager(self.layout.groups, page_size, num_pages)
+        self.storage = CacheStorage(self.layout, [LayerRun(0)], page_size, [num_pages], 0, dtype, "cuda")
+        self.storage.pages[0].fill_(float("nan"))
+        self.builder = BatchBuilder(self.cm, vocab, "cuda", 512, 8, 64)
+
+    def batch(self, items):
+        from nanohybrid_vlm_b200.engine.batch import StepItem
+        built = []
+        for rid, start, n in items:
+            self.cm.allocate(rid, start + n)
+            built.append(StepItem(rid, [0] * n, start, []))
+        b = self.builder.build(built)
+        return b, self.storage.view(0, None, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from nanohybrid_vlm_b200.parts import NORMS, part
+    norm, w = build_part(NORMS, part("rmsnorm", width=96, eps=1e-5), 96, dtype)
+    g = torch.Generator().manual_seed(1)
+    x, r = torch.randn(7, 96, generator=g).to(dtype), torch.randn(7, 96, generator=g).to(dtype)
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(norm.forward(x.cuda()).cpu().float(), plain.rms_norm(x, w["weight"], 1e-5).float(), **tol)
+    res = r.clone().cuda()
+    y, new_r = plain.add_rms_norm(x, r, w["weight"], 1e-5)
+    torch.testing.assert_close(norm.forward_add(x.cuda(), res).cpu().float(), y.float(), **tol)
+    torch.testing.assert_close(res.cpu().float(), new_r.float(), **tol)
+    rows = torch.tensor([6, 2], dtype=torch.int32).cuda()
+    torch.testing.assert_close(norm.forward_add_rows(x.cuda(), r.cuda(), rows).cpu().float(), y[[6, 2]].float(), **tol)
+    # a norm stored as an offset from one
+    off, w = build_part(NORMS, part("rmsnorm", width=96, eps=1e-5, weight_offset=1.0), 96, dtype)
+    torch.testing.assert_close(off.forward(x.cuda()).cpu().float(),
+                               plain.rms_norm(x, (1 + w["weight"].float()).to(dtype), 1e-5).float(), **tol)
+
+
+def test_position_part_shares_one_table():
+    from nanohybrid_vlm_b200.parts import BuildEnv, part
+    env = BuildEnv(64, torch.float32, "cuda", 300)
+    spec = part("rope", theta=5000.0, rotary_dim=24, max_position=300)
+    a, b = env.position(spec), env.position(part("rope", theta=5000.0, rotary_dim=24, max_position=300))
+    assert a is b and env.position(None) is None
+    table, rot = a.rotary()
+    cos, sin = plain.rope_table(24, 300, 5000.0)
+    assert rot == 24 and torch.equal(table.cpu(), torch.cat((cos, sin), -1))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,hidden", [(6, 2, 32, 96), (4, 4, 16, 80)])
+def test_attention_part_whole_and_in_portions(dtype, nq, nkv, d, hidden):
+    from nanohybrid_vlm_b200.parts import MIXERS, part
+    rope = part("rope", theta=10000.0, rotary_dim=d, max_position=256)
+    spec = part("gqa_attention", num_heads=nq, num_kv_heads=nkv, head_dim=d, qk_norm_eps=1e-6, position=rope)
+    mixer, w = build_part(MIXERS, spec, hidden, dtype)
+    T = 45
+    x = (torch.randn(T, hidden, generator=torch.Generator().manual_seed(2))).to(dtype)
+    names = {"q_proj.weight": w["qkv_proj.weight"][:nq * d], "k_proj.weight": w["qkv_proj.weight"][nq * d:(nq + nkv) * d],
+             "v_proj.weight": w["qkv_proj.weight"][(nq + nkv) * d:], "o_proj.weight": w["o_proj.weight"],
+             "q_norm.weight": w["q_norm.weight"], "k_norm.weight": w["k_norm.weight"]}
+    cfg = dict(num_attention_heads=nq, num_key_value_heads=nkv, head_dim=d, rms_norm_eps=1e-6)
+    cos, sin = plain.rope_table(d, 256, 10000.0)
+    ref = plain.attention_mixer(x, torch.arange(T), names, "", cfg, cos, sin).float()
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-3)
+    env = OneRequest(mixer.cache_need(), dtype=dtype)
+    b, view = env.batch([("whole", 0, T)])
+    torch.testing.assert_close(mixer.forward(x.cuda(), b, view).cpu().float(), ref, **tol)
+    got, at = [], 0
+    for n in (13, 2, 29, 1):
+        b, view = env.batch([("cut", at, n)])
+        got.append(mixer.forward(x[at:at + n].cuda(), b, view).cpu().float())
+        at += n
+    torch.testing.assert_close(torch.cat(got), ref, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from nanohybrid_vlm_b200.parts import FEED_FORWARDS, part
+    ffn, w = build_part(FEED_FORWARDS, part("swiglu", intermediate_size=160), 96, dtype)
+    x = torch.randn(9, 96, generator=torch.Generator().manual_seed(3)).to(dtype)
+    names = {"gate_proj.weight": w["gate_up_proj.weight"][:160], "up_proj.weight": w["gate_up_proj.weight"][160:],
+             "down_proj.weight": w["down_proj.weight"]}
+    tol = dict(rtol=1e-4, atol=1e-6) if dtype == torch.float32 else dict(rtol=3e-2, atol=1e-3)
+    torch.testing.assert_close(ffn.forward(x.cuda(), None).cpu().float(), plain.swiglu_mlp(x, names, "").float(), **tol)
+
+
+def test_embedding_and_head_parts():
+    from nanohybrid_vlm_b200.parts.embedding import LMHead, TokenEmbedding
+    from nanohybrid_vlm_b200.parts import BuildEnv, part
+    env = BuildEnv(48, torch.float32, "cuda", 64)
+    emb = TokenEmbedding(part("token_embedding", vocab_size=101), env)
+    table = torch.randn(101, 48, generator=torch.Generator().manual_seed(4))
+    emb.bind({"weight": table.cuda()})
+    ids = torch.tensor([5, 100, 0, 5], dtype=torch.int32)
+    assert torch.equal(emb.forward(ids.cuda()).cpu(), table[ids.long()])
+    head = LMHead(part("lm_head", vocab_size=101, tied=True), env)
+    assert head.params() == []
+    head.tie(emb.w_weight)
+    x = torch.randn(3, 48, generator=torch.Generator().manual_seed(5))
+    torch.testing.assert_close(head.forward(x.cuda()).cpu(), x @ table.t(), rtol=1e-5, atol=1e-5)
+
+
+# ------------------------------------------------------------------------------------------------ toy architecture
+
+TOY = dict(architectures=["ToyStateLM"], model_type="toy_state", hidden_size=48, vocab_size=97, state_decay=0.75,
+           num_attention_heads=3, num_key_value_heads=1, head_dim=16, intermediate_size=64, rms_norm_eps=1e-5,
+           rope_theta=1000.0, max_position_embeddings=128, torch_dtype="float32")
+
+
+def register_toy():
+    """A mixer with state of its own (an exponential moving average of its inputs, kept per request in a
+    slot) and an architecture that uses it, both defined here."""
+    from nanohybrid_vlm_b200.config import ModelConfig, register_architecture
+    from nanohybrid_vlm_b200.parts import (MIXERS, FixedStateNeed, LayerRun, LayerSpec, Mixer, ModelSpec, ParamDecl,
+                                           PartUse, part)
+
+    class MovingAverageMixer(Mixer):
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.decay = float(spec["decay"])
+
+        def params(self):
+            H = self.env.hidden_size
+            return [ParamDecl("out.weight", (H, H))]
+
+        def cache_need(self):
+            return FixedStateNeed((self.env.hidden_size,), "float32")
+
+        def forward(self, x, batch, cache):
+            y = torch.empty_like(x)
+            slots = batch.state_slots.tolist()
+            for s in range(batch.n_seqs):
+                a, b = batch.host_cu_q[s], batch.host_cu_q[s + 1]
+                if slots[s] < 0:
+                    y[a:b] = 0
+                    continue
+                state = cache.state[slots[s]]
+                if batch.host_kv_len[s] - (b - a) == 0:      # the request starts: its slot may hold another's state
+                    state.zero_()
+                for t in range(a, b):
+                    state.mul_(self.decay).add_(x[t].float(), alpha=1 - self.decay)
+                    y[t] = (self.w_out_weight.float() @ state).to(x.dtype)
+            return y
+
+    MIXERS.register("moving_average", MovingAverageMixer, replace=True)
+
+    def parse(raw):
+        cfg = ModelConfig(architecture="ToyStateLM", model_type=raw["model_type"], vocab_size=raw["vocab_size"],
+                          hidden_size=raw["hidden_size"], max_position_embeddings=raw["max_position_embeddings"],
+                          dtype=torch.float32, eos_token_id=None)
+        object.__setattr__(cfg, "raw", raw)
+        return cfg
+
+    def build(cfg):
+        raw = cfg.raw
+        H = raw["hidden_size"]
+        norm = part("rmsnorm", width=H, eps=raw["rms_norm_eps"])
+        ffn = part("swiglu", intermediate_size=raw["intermediate_size"])
+        rope = part("rope", theta=raw["rope_theta"], rotary_dim=raw["head_dim"], max_position=raw["max_position_embeddings"])
+        attn = part("gqa_attention", num_heads=raw["num_attention_heads"], num_kv_heads=raw["num_key_value_heads"],
+                    head_dim=raw["head_dim"], qk_norm_eps=raw["rms_norm_eps"], position=rope)
+        avg = part("moving_average", decay=raw["state_decay"])
+
+        def layer(i, mixer):
+            return LayerSpec(part("prenorm_residual"), PartUse(mixer, f"layers.{i}.mixer."), PartUse(norm, f"layers.{i}.norm1."),
+                             PartUse(ffn, f"layers.{i}.ffn."), PartUse(norm, f"layers.{i}.norm2."))
+
+        return ModelSpec(architecture="ToyStateLM", hidden_size=H, vocab_size=raw["vocab_size"],
+                         max_position=raw["max_position_embeddings"],
+                         embedding=PartUse(part("token_embedding", vocab_size=raw["vocab_size"]), "embed."),
+                         layers=(layer(0, avg), layer(1, attn)),
+                         # layer 0 runs twice (its second run has a state of its own); the last run reads the keys
+                         # and values that the first attention run stored
+                         order=(LayerRun(0), LayerRun(1), LayerRun(0), LayerRun(1, cache_from=1)),
+                         final_norm=PartUse(norm, "final_norm."),
+                         head=PartUse(part("lm_head", vocab_size=raw["vocab_size"], tied=False), "head."))
+
+    register_architecture("ToyStateLM", model_types=("toy_state",), parse_config=parse, build_spec=build, replace=True)
+
+
+def toy_plain_logits(w, tokens):
+    """The toy model over one whole sequence, written out plainly."""
+    raw, T = TOY, len(tokens)
+    nq, nkv, d, eps = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], raw["rms_norm_eps"]
+    cos, sin = plain.rope_table(d, raw["max_position_embeddings"], raw["rope_theta"])
+    pos = torch.arange(T)
+    h = w["embed.weight"][torch.tensor(tokens)]
+
+    def average(x, i):
+        s, out = torch.zeros(raw["hidden_size"]), []
+        for t in range(T):
+            s = raw["state_decay"] * s + (1 - raw["state_decay"]) * x[t]
+            out.append(w[f"layers.{i}.mixer.out.weight"] @ s)
+        return torch.stack(out)
+
+    def qkv(x, i):
+        p = f"layers.{i}.mixer."
+        q = plain.linear(x, w[p + "q_proj.weight"]).view(T, nq, d)
+        k = plain.linear(x, w[p + "k_proj.weight"]).view(T, nkv, d)
+        v = plain.linear(x, w[p + "v_proj.weight"]).view(T, nkv, d)
+        q = plain.apply_rope(plain.rms_norm(q, w[p + "q_norm.weight"], eps), cos[pos], sin[pos])
+        k = plain.apply_rope(plain.rms_norm(k, w[p + "k_norm.weight"], eps), cos[pos], sin[pos])
+        return q, k, v
+
+    residual, kept = None, None
+    for run, (i, kind) in enumerate([(0, "avg"), (1, "attn"), (0, "avg"), (1, "shared")]):
+        if residual is None:
+            residual, x = h, plain.rms_norm(h, w[f"layers.{i}.norm1.weight"], eps)
+        else:
+            x, residual = plain.add_rms_norm(h, residual, w[f"layers.{i}.norm1.weight"], eps)
+        if kind == "avg":
+            a = average(x, i)
+        else:
+            q, k, v = qkv(x, i)
+            if kind == "attn":
+                kept = (k, v)
+            o = plain.causal_attention(q, kept[0], kept[1], d ** -0.5)
+            a = plain.linear(o.reshape(T, nq * d), w[f"layers.{i}.mixer.o_proj.weight"])
+        x, residual = plain.add_rms_norm(a, residual, w[f"layers.{i}.norm2.weight"], eps)
+        h = plain.swiglu_mlp(x, w, f"layers.{i}.ffn.")
+    x, _ = plain.add_rms_norm(h, residual, w["final_norm.weight"], eps)
+    return plain.linear(x, w["head.weight"])
+
+
+def test_toy_architecture_with_a_state_mixer_registers_builds_and_steps(tmp_path):
+    from safetensors.torch import load_file
+    from nanohybrid_vlm_b200.config import ARCHITECTURES, Config
+    from nanohybrid_vlm_b200.engine import ModelRunner, StepItem
+    from nanohybrid_vlm_b200.parts import MIXERS
+    from nanohybrid_vlm_b200.weights import write_random_model
+    register_toy()
+    try:
+        d = write_random_model(str(tmp_path / "toy"), TOY, seed=9)
+        w = load_file(f"{d}/model.safetensors")
+        assert "layers.0.mixer.out.weight" in w and "layers.1.mixer.k_proj.weight" in w
+        runner = ModelRunner(Config(d, kvcache_block_size=4, num_kvcache_blocks=40, max_num_seqs=3,
+                                    max_num_batched_tokens=64, max_model_len=128, enforce_eager=True))
+        assert runner.cache.slots is not None and runner.cache.slots.num_slots == 3       # state slots appeared
+        assert [g.window for g in runner.layout.groups] == [None]
+        assert runner.layout.run_group == [None, 0, None, None]
+        rng = np.random.default_rng(0)
+        reqs = {r: rng.integers(0, TOY["vocab_size"], n).tolist() for r, n in (("a", 30), ("b", 17), ("c", 41), ("d", 9))}
+        ref = {r: toy_plain_logits(w, t) for r, t in reqs.items()}
+        # a, b, c in portions of different sizes side by side; d takes over a finished request's slot and pages
+        plan = {"a": [7, 2, 21], "b": [1, 1, 15], "c": [20, 20, 1]}
+        at = {r: 0 for r in reqs}
+        got = {r: [] for r in reqs}
+        for step in range(3):
+            items = []
+            for r, cuts in plan.items():
+                n = cuts[step]
+                runner.cache.allocate(r, at[r] + n)
+                items.append(StepItem(r, reqs[r][at[r]:at[r] + n], at[r], list(range(n))))
+                at[r] += n
+            logits = runner.step(items).cpu()
+            k = 0
+            for it in items:
+                got[it.req_id].append(logits[k:k + len(it.tokens)])
+                k += len(it.tokens)
+        runner.cache.free("b")
+        runner.cache.allocate("d", 9)
+        assert runner.cache.state_slot("d") == 1                                           # b's slot, reused
+        got["d"].append(runner.step([StepItem("d", reqs["d"], 0, list(range(9)))]).cpu())
+        for r in reqs:
+            torch.testing.assert_close(torch.cat(got[r]), ref[r], rtol=1e-4, atol=2e-5)
+        runner.cache.check()
+    finally:
+        ARCHITECTURES.unregister("ToyStateLM")
+        MIXERS.unregister("moving_average")
