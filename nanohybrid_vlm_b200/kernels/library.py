@@ -26,6 +26,7 @@ _SIGNATURES = {
     "nhv_attention_simt": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, F, P],
     "nhv_gemm_nt_simt": [I, P, P, P, I, I, I, I, I, I, I, P],
     "nhv_sample": [P, P, I, P, P, P, I, I, P],
+    "nhv_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, P],
 }
 
 

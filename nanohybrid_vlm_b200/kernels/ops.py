@@ -176,6 +176,9 @@ def linear(out, x, weight) -> None:
         assert out.dtype == torch.float32
         call("nhv_gemm_nt_simt", F32, out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K, N, 0,
              stream_ptr())
+    elif small_m_ok(x, weight):
+        call("nhv_gemm_small_m", out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), N,
+             int(out.dtype == torch.float32), 0, stream_ptr())
     elif out.dtype == torch.float32:
         # the product is rounded to bfloat16 and then widened, as the reference's head does
         # (nanovllm/layers/embed_head.py:61, nanovllm/layers/sampler.py:12)
@@ -184,6 +187,29 @@ def linear(out, x, weight) -> None:
         to_f32(out, tmp)
     else:
         torch.mm(x, weight.t(), out=out)
+
+
+SMALL_M = 16    # up to this many tokens the weight-streaming kernel runs instead of the library product
+
+
+def small_m_ok(x, weight) -> bool:
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def swiglu_first_half(act, x, gate_up_weight) -> bool:
+    """act[M, I] = silu(x Wg^T) * (x Wu^T) in one kernel when the batch is small enough for the
+    weight-streaming kernel (gate_up_weight [2 I, K], gate rows first).  Returns False if it did not run."""
+    if not small_m_ok(x, gate_up_weight):
+        return False
+    _need_cuda(act, x, gate_up_weight)
+    _contig("act", act); _contig("gate_up_weight", gate_up_weight)
+    M, K = x.shape
+    inter = gate_up_weight.shape[0] // 2
+    assert act.shape == (M, inter) and act.dtype == torch.bfloat16 and gate_up_weight.shape[1] == K
+    call("nhv_gemm_small_m", act.data_ptr(), x.data_ptr(), gate_up_weight.data_ptr(), M, inter, K, x.stride(0), inter,
+         2, inter, stream_ptr())
+    return True
 
 
 def linear_simt(out, x, weight) -> None:

@@ -26,10 +26,11 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, batch):
         T = x.shape[0]
-        gate_up = self.new(T, 2 * self.inter)
-        ops.linear(gate_up, x, self.w_gate_up_proj_weight)
         act = self.new(T, self.inter)
-        ops.silu_mul(act, gate_up)
+        if not ops.swiglu_first_half(act, x, self.w_gate_up_proj_weight):
+            gate_up = self.new(T, 2 * self.inter)
+            ops.linear(gate_up, x, self.w_gate_up_proj_weight)
+            ops.silu_mul(act, gate_up)
         y = self.new(T, self.env.hidden_size)
         ops.linear(y, act, self.w_down_proj_weight)
         return y

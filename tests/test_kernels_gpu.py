@@ -117,6 +117,37 @@ def test_linear(ops, dtype, M, N, K):
     torch.testing.assert_close(out32.cpu(), ref, **t)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(384, 96), (1000, 264), (4096, 4096), (24577, 520), (50, 12288)])
+def test_gemm_small_m(ops, M, N, K):
+    """The decode step's weight-streaming product: plain, with float32 output, and the feed-forward's
+    first half fused with its activation."""
+    g = torch.Generator().manual_seed(30)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    assert ops.small_m_ok(dev(x), dev(w))
+    ref = (x.double() @ w.double().t()).float()
+    t = dict(rtol=2e-2, atol=2e-2 * ref.abs().max().item() / 4)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear(out, dev(x), dev(w))
+    torch.testing.assert_close(out.cpu().float(), ref, **t)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    ops.linear(out32, dev(x), dev(w))
+    assert torch.equal(out32.cpu(), out.cpu().float())           # the float32 form is the bfloat16 one, widened
+    if N % 2 == 0:
+        inter = N // 2
+        act = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+        assert ops.swiglu_first_half(act, dev(x), dev(w))
+        gu = out.cpu().float()
+        want = (gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]).to(torch.bfloat16)
+        torch.testing.assert_close(act.cpu().float(), want.float(), rtol=1e-2, atol=1e-3)
+    # a row's result does not depend on the other tokens of the batch
+    if M > 1:
+        one = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+        ops.linear(one, dev(x[M - 1:M]), dev(w))
+        assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
+
+
 def make_pages(k, v, page_size, n_pages, rng, dtype):
     """Scatter one request's keys/values [T, nkv, d] over shuffled pages. Returns pages tensor and table."""
     T, nkv, d = k.shape
