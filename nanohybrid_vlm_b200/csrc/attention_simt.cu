@@ -35,6 +35,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
                                        int n_seqs, int nq, int nkv, int d, int page_size, int n_pages, int window,
                                        float scale, int TQ, int GS) {
   extern __shared__ float smem[];
+  pdl_prologue();
   const int G = nq / nkv;
   const int kvh = blockIdx.y;
   const int g0 = blockIdx.z * GS;
@@ -192,7 +193,7 @@ NHV_API int nhv_attention_simt(int dtype, const void* q, int q_stride, void* out
     if (smem > 48 * 1024)                                                                                      \
       NHV_CUDA(cudaFuncSetAttribute(attn_paged_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                     (int)smem), "attention");                                                  \
-    attn_paged_simt_kernel<T><<<grid, AT_WARPS * 32, smem, stream>>>(                                          \
+    nhv_launch(attn_paged_simt_kernel<T>, grid, AT_WARPS * 32, smem, stream,                                   \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv_pages, block_table, bt_stride, cu_q, kv_len,  \
         n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS);                                        \
   } while (0)

@@ -26,6 +26,7 @@ NHV_API int nhv_abi_version() { return 1; }
 template <typename T>
 __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
                              int width, int vocab) {
+  pdl_prologue();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -40,10 +41,10 @@ NHV_API int nhv_embed(int dtype, void* out, const void* table, const int* ids, i
   NHV_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embed: bad sizes");
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == NHV_F32)
-    embed_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)out, (const float*)table, ids, width, vocab);
+    nhv_launch(embed_kernel<float>, n_tokens, threads, 0, stream, (float*)out, (const float*)table, ids, width, vocab);
   else if (dtype == NHV_BF16)
-    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)table,
-                                                                 ids, width, vocab);
+    nhv_launch(embed_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (__nv_bfloat16*)out,
+               (const __nv_bfloat16*)table, ids, width, vocab);
   else
     NHV_REQUIRE(false, "embed: unknown dtype %d", dtype);
   NHV_CHECK_LAUNCH("embed");
@@ -60,6 +61,7 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, T* 
                                int write_residual, float weight_offset) {
   extern __shared__ float row[];
   __shared__ float red[33];
+  pdl_prologue();
   const int r = blockIdx.x;
   const size_t src = (size_t)(rows ? rows[r] : r) * width;
   float ss = 0.f;
@@ -97,8 +99,8 @@ NHV_API int nhv_rmsnorm(int dtype, void* out, const void* x, void* residual, con
     if (smem > 48 * 1024)                                                                                  \
       NHV_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
                                     (int)smem), "rmsnorm");                                                \
-    rmsnorm_kernel<T><<<n_rows, threads, smem, stream>>>((T*)out, (const T*)x, (T*)residual, (const T*)w,  \
-                                                        rows, width, eps, write_residual, weight_offset); \
+    nhv_launch(rmsnorm_kernel<T>, n_rows, threads, smem, stream, (T*)out, (const T*)x, (T*)residual,    \
+               (const T*)w, rows, width, eps, write_residual, weight_offset);                            \
   } while (0)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
@@ -112,6 +114,7 @@ NHV_API int nhv_rmsnorm(int dtype, void* out, const void* x, void* residual, con
 // gate_up [n, 2*inter] with gate in the first half of each row; out [n, inter].
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
+  pdl_prologue();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / inter;
     const int c = (int)(i - t * inter);
@@ -124,6 +127,7 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
 // bf16, inter a multiple of 8: 16-byte loads and stores.
 __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
                                        int inter8, size_t total8) {
+  pdl_prologue();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / inter8;
     const int c = (int)(i - t * inter8);
@@ -150,15 +154,15 @@ NHV_API int nhv_silu_mul(int dtype, void* out, const void* gate_up, int n_rows, 
   if (dtype == NHV_BF16 && inter % 8 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)gate_up % 16 == 0)) {
     const size_t total8 = total / 8;
     const int blocks = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
-    silu_mul_bf16x8_kernel<<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,
-                                                          inter / 8, total8);
+    nhv_launch(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,
+               inter / 8, total8);
   } else {
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (dtype == NHV_F32)
-      silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+      nhv_launch(silu_mul_kernel<float>, blocks, threads, 0, stream, (float*)out, (const float*)gate_up, inter, total);
     else if (dtype == NHV_BF16)
-      silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out,
-                                                                    (const __nv_bfloat16*)gate_up, inter, total);
+      nhv_launch(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out,
+                 (const __nv_bfloat16*)gate_up, inter, total);
     else
       NHV_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
   }
@@ -169,6 +173,7 @@ NHV_API int nhv_silu_mul(int dtype, void* out, const void* gate_up, int n_rows, 
 // ---------------------------------------------------------------- storage type -> fp32 rows
 template <typename T>
 __global__ void to_f32_kernel(float* __restrict__ out, const T* __restrict__ x, size_t total) {
+  pdl_prologue();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
     out[i] = to_f32<T>(x[i]);
 }
@@ -178,9 +183,9 @@ NHV_API int nhv_to_f32(int dtype, float* out, const void* x, size_t total, cudaS
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == NHV_BF16)
-    to_f32_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(out, (const __nv_bfloat16*)x, total);
+    nhv_launch(to_f32_kernel<__nv_bfloat16>, blocks, threads, 0, stream, out, (const __nv_bfloat16*)x, total);
   else if (dtype == NHV_F32)
-    to_f32_kernel<float><<<blocks, threads, 0, stream>>>(out, (const float*)x, total);
+    nhv_launch(to_f32_kernel<float>, blocks, threads, 0, stream, out, (const float*)x, total);
   else
     NHV_REQUIRE(false, "to_f32: unknown dtype %d", dtype);
   NHV_CHECK_LAUNCH("to_f32");

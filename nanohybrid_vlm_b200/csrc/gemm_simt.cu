@@ -14,6 +14,7 @@ __global__ void __launch_bounds__(256) gemm_nt_simt_kernel(TO* __restrict__ C, c
                                                            int ldw, int ldc) {
   __shared__ __align__(16) float As[GK][GM + 4];
   __shared__ __align__(16) float Ws[GK][GN + 4];
+  pdl_prologue();
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, 4 x 4 outputs each
   const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
   float acc[4][4];
@@ -71,14 +72,14 @@ NHV_API int nhv_gemm_nt_simt(int dtype, void* C, const void* A, const void* W, i
   dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM);
   NHV_REQUIRE(grid.y <= 65535, "gemm: M=%d is beyond the grid's reach", M);
   if (dtype == NHV_F32)
-    gemm_nt_simt_kernel<float, float><<<grid, 256, 0, stream>>>((float*)C, (const float*)A, (const float*)W, M, N, K,
-                                                                lda, ldw, ldc);
+    nhv_launch(gemm_nt_simt_kernel<float, float>, grid, 256, 0, stream, (float*)C, (const float*)A, (const float*)W, M, N,
+               K, lda, ldw, ldc);
   else if (dtype == NHV_BF16 && out_f32)
-    gemm_nt_simt_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(
-        (float*)C, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
+    nhv_launch(gemm_nt_simt_kernel<__nv_bfloat16, float>, grid, 256, 0, stream, (float*)C, (const __nv_bfloat16*)A,
+               (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
   else if (dtype == NHV_BF16)
-    gemm_nt_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(
-        (__nv_bfloat16*)C, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
+    nhv_launch(gemm_nt_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, (__nv_bfloat16*)C,
+               (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
   else
     NHV_REQUIRE(false, "gemm: unknown dtype %d", dtype);
   NHV_CHECK_LAUNCH("gemm_nt_simt");

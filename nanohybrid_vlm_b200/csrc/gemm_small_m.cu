@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(THREADS) gemm_small_m_kernel(void* __restrict_
                                                                const bf16* __restrict__ W, int M, int N, int K,
                                                                int lda, int ldc, int up_row_offset) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_prologue();
   constexpr int W_ROWS = MT * 16, X_ROWS = NT * 8;
   constexpr int STAGE_ELEMS = (W_ROWS + X_ROWS) * ROW_CH * 8;
   bf16* ring = reinterpret_cast<bf16*>(smem_raw);
@@ -178,7 +179,8 @@ int launch(void* y, const bf16* x, const bf16* W, int M, int N, int K, int lda, 
   }
   const int rows_per_block = MODE == 2 ? 16 : W_ROWS;
   const int blocks = (N + rows_per_block - 1) / rows_per_block;
-  gemm_small_m_kernel<MT, NT, STAGES, MODE><<<blocks, THREADS, smem, stream>>>(y, x, W, M, N, K, lda, ldc, up_row_offset);
+  nhv_launch(gemm_small_m_kernel<MT, NT, STAGES, MODE>, blocks, THREADS, smem, stream, y, x, W, M, N, K, lda, ldc,
+             up_row_offset);
   NHV_CHECK_LAUNCH("gemm_small_m");
   return 0;
 }

@@ -1,0 +1,434 @@
+// y[M,N] = x[M,K] * W[N,K]^T in bfloat16 for up to 16 tokens: the decode step's projections,
+// where the whole job is to read W once at the speed of HBM.
+//
+// Persistent, stream-K: the grid is one block per SM.  The work is cut into units of (64 rows
+// of W) x (BK columns); unit u = tile * (K / BK) + k-block, and block c owns the contiguous
+// units [c * U / G, (c + 1) * U / G), so every SM reads the same number of bytes whatever N and
+// K are.  A producer thread streams its units through a ring of shared-memory stages with TMA
+// tensor copies (cp.async.bulk.tensor.2d, boxes of 64 columns x 64 rows in the 128-byte swizzle,
+// completion counted in bytes on an mbarrier; rows and columns beyond the matrix arrive as
+// zeros); four consumer warps take a quarter of each stage's columns
+// each (mma.sync.m16n8k16, W rows on the MMA's M axis, tokens on its N axis, fp32
+// accumulators).  At the end of a tile the four warps' sums are added through shared memory.  A
+// block that owns all k-blocks of a tile writes the result; otherwise it stores its partial sums
+// to scratch, and the block that arrives last at the tile's counter adds all partials in block
+// order and writes the result: no block ever waits for another, and the order of the sums is
+// fixed.
+//
+// The kernel is launched with programmatic dependent launch: it starts while the kernel before
+// it in the stream is still running, fills its ring with weights (which no kernel writes), and
+// only then waits for that kernel (griddepcontrol.wait) before it reads x or writes anything.
+//
+// Modes: 0: y bf16.  1: y fp32, rounded through bf16 as nanovllm/layers/embed_head.py:61 with
+// nanovllm/layers/sampler.py:12 gives logits.  2: W = [gate rows; up rows], y = silu(gate) * up
+// (nanovllm/layers/activation.py:9-11), both products rounded to bf16 first: a tile is 32 gate
+// rows and the same 32 rows of up.  W is [out, in] row-major (nanovllm/layers/linear.py:40,66).
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host
+// reads with nhv_gemm_stream_k_error().
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "nhv_common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int ROWS = 64;                 // weight rows per tile (4 MMA row tiles)
+constexpr int MT = ROWS / 16;
+constexpr int CONSUMER_WARPS = 4;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+__device__ int g_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: false (and the error word set) if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  atomicExch(&g_error, code);
+  return false;
+}
+// One box of the tensor described by `map`, starting at column x (a multiple of 8) and row y.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+               ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { pdl_wait(); }
+__device__ __forceinline__ void launch_dependents() { pdl_launch_dependents(); }
+
+// After a wait ran out: give copies that may still be in flight time to land before the block leaves.
+__device__ __forceinline__ void give_up_delay() {
+  for (int i = 0; i < 2000; ++i) __nanosleep(200);
+}
+
+constexpr int BK = 256;                  // columns per stage
+constexpr int BOX_COLS = 64;             // columns per TMA box: 128 bytes, the widest the 128-byte swizzle takes
+constexpr int BOXES = BK / BOX_COLS;
+
+struct alignas(64) Params {
+  CUtensorMap w_map;    // W [N, K], box 64 columns x 64 rows (mode 2: x 32 rows)
+  CUtensorMap x_map;    // x [M, K], box 64 columns x (8 or 16) rows
+  void* y;
+  const bf16* x;
+  const bf16* W;
+  float* scratch;       // [grid][2][ROWS][8 * NT] partial sums
+  int* counters;        // [tiles], zero between launches
+  int M, N, K, lda, ldc, mode, up_row_offset;
+};
+
+__device__ __forceinline__ long long unit_begin(int c, long long total, int G) { return (long long)c * total / G; }
+__device__ __forceinline__ int unit_owner(long long u, long long total, int G) { return (int)(((u + 1) * G - 1) / total); }
+
+template <int NT, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1) gemm_stream_k_kernel(const __grid_constant__ Params p) {
+  constexpr int X_ROWS = NT * 8;
+  constexpr int W_BOX_BYTES = ROWS * 128, X_BOX_BYTES = X_ROWS * 128;
+  constexpr int STAGE_BYTES = BOXES * (W_BOX_BYTES + X_BOX_BYTES);     // W boxes first, then x boxes
+  extern __shared__ unsigned char smem_unaligned[];
+  // the swizzle pattern repeats every 1024 bytes: boxes must start on such a boundary
+  unsigned char* smem = smem_unaligned + ((1024 - (smem_u32(smem_unaligned) & 1023)) & 1023);
+  unsigned char* ring = smem;
+  float* red = reinterpret_cast<float*>(smem + (size_t)STAGES * STAGE_BYTES);       // [4][ROWS][X_ROWS]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + CONSUMER_WARPS * ROWS * X_ROWS);
+  uint64_t* empty = full + STAGES;
+  __shared__ int s_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = gridDim.x, c = blockIdx.x;
+  const int out_rows = p.mode == 2 ? ROWS / 2 : ROWS;       // result columns per tile
+  const int tiles = (p.N + out_rows - 1) / out_rows;
+  const int kb = (p.K + BK - 1) / BK;
+  const long long total = (long long)tiles * kb;
+  const long long u0 = unit_begin(c, total, G), u1 = unit_begin(c + 1, total, G);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], CONSUMER_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+  launch_dependents();
+
+  if (warp == CONSUMER_WARPS) {
+    // ---------------------------------------------------------------- producer (one thread)
+    if (lane == 0) {
+      const long long n_units = u1 - u0;
+      auto issue_w = [&](long long i) {
+        const long long u = u0 + i;
+        const int tile = (int)(u / kb), k = (int)(u - (long long)tile * kb);
+        const int s = (int)(i % STAGES);
+        unsigned char* dst = ring + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);                 // zero-filled parts of a box count too
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b) {
+          const int col = k * BK + b * BOX_COLS;
+          if (p.mode == 2) {     // 32 gate rows, then the same 32 rows of up
+            tma_load_2d(dst + b * W_BOX_BYTES, &p.w_map, col, tile * (ROWS / 2), &full[s]);
+            tma_load_2d(dst + b * W_BOX_BYTES + W_BOX_BYTES / 2, &p.w_map, col, p.up_row_offset + tile * (ROWS / 2), &full[s]);
+          } else {
+            tma_load_2d(dst + b * W_BOX_BYTES, &p.w_map, col, tile * ROWS, &full[s]);
+          }
+        }
+      };
+      auto issue_x = [&](long long i) {
+        const int k = (int)((u0 + i) % kb);
+        const int s = (int)(i % STAGES);
+        unsigned char* dst = ring + (size_t)s * STAGE_BYTES + BOXES * W_BOX_BYTES;
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b) tma_load_2d(dst + b * X_BOX_BYTES, &p.x_map, k * BK + b * BOX_COLS, 0, &full[s]);
+      };
+      // Fill the ring with weights while the kernel before this one may still be running, then wait for it.
+      const int pre = (int)min((long long)STAGES, n_units);
+      for (int i = 0; i < pre; ++i) issue_w(i);
+      grid_dependency_wait();
+      for (int i = 0; i < pre; ++i) issue_x(i);
+      bool ok = true;
+      for (long long i = STAGES; i < n_units; ++i) {
+        const int s = (int)(i % STAGES);
+        ok = mbar_wait(&empty[s], (uint32_t)((i / STAGES) - 1) & 1, 1);
+        if (!ok) break;
+        issue_w(i);
+        issue_x(i);
+      }
+      if (!ok) give_up_delay();
+    } else {
+      grid_dependency_wait();
+    }
+  } else {
+    // ---------------------------------------------------------------- consumers
+    grid_dependency_wait();
+    float acc[MT][NT][4];
+    auto clear = [&]() {
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    };
+    clear();
+    constexpr int KSTEPS = BK / 16 / CONSUMER_WARPS;        // k-steps per warp per stage: one box per warp
+    static_assert(KSTEPS * 16 == BOX_COLS, "each consumer warp takes one box of a stage");
+    bool ok = true;
+    for (long long u = u0; u < u1 && ok; ++u) {
+      const long long i = u - u0;
+      const int s = (int)(i % STAGES);
+      const int tile = (int)(u / kb), k = (int)(u - (long long)tile * kb);
+      ok = mbar_wait(&full[s], (uint32_t)(i / STAGES) & 1, 2);
+      if (!ok) { give_up_delay(); break; }
+      // this warp's box of the stage; inside a box row r holds its 16-byte chunk c at chunk (c ^ (r & 7))
+      const unsigned char* ws = ring + (size_t)s * STAGE_BYTES + warp * W_BOX_BYTES;
+      const unsigned char* xs = ring + (size_t)s * STAGE_BYTES + BOXES * W_BOX_BYTES + warp * X_BOX_BYTES;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const int c0 = kk * 2;
+        uint32_t b[4];
+        {
+          const int r = NT == 1 ? (lane & 7) : (lane & 7) + ((lane >> 4) << 3);
+          const int ch = c0 + ((lane >> 3) & 1);
+          ldmatrix_x4(b, xs + r * 128 + ((ch ^ (r & 7)) << 4));
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          uint32_t a[4];
+          const int r = mt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+          const int ch = c0 + (lane >> 4);
+          ldmatrix_x4(a, ws + r * 128 + ((ch ^ (r & 7)) << 4));
+          mma_bf16(acc[mt][0], a, b[0], b[1]);
+          if (NT == 2) mma_bf16(acc[mt][NT - 1], a, b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+
+      const bool tile_ends = k == kb - 1 || u == u1 - 1;
+      if (!tile_ends) continue;
+      // ------------------------------------------------------------ end of this block's piece of the tile
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = mt * 16 + (lane >> 2) + ((e >> 1) << 3);
+            const int m = j * 8 + ((lane & 3) << 1) + (e & 1);
+            red[(warp * ROWS + r) * X_ROWS + m] = acc[mt][j][e];
+          }
+      clear();
+      consumer_sync();
+      const long long t_first = (long long)tile * kb, t_last = t_first + kb - 1;
+      const bool whole = u0 <= t_first && u1 > t_last;
+      const int tid = threadIdx.x;                            // 0..127
+      float* mine = nullptr;
+      int pieces = 1, c_first = c;
+      if (!whole) {
+        c_first = unit_owner(t_first, total, G);
+        pieces = unit_owner(t_last, total, G) - c_first + 1;
+        // slot 0: the tile this block's range starts in; slot 1: a later tile that it only begins
+        const int slot = (int)(u0 / kb) == tile ? 0 : 1;
+        mine = p.scratch + ((size_t)c * 2 + slot) * ROWS * X_ROWS;
+        for (int id = tid; id < ROWS * X_ROWS; id += CONSUMER_WARPS * 32) {
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[w * ROWS * X_ROWS + id];
+          mine[id] = v;
+        }
+        __threadfence();
+        consumer_sync();
+        if (tid == 0) s_flag = atomicAdd(&p.counters[tile], 1);
+        consumer_sync();
+        if (s_flag != pieces - 1) { consumer_sync(); continue; }   // another block will finish this tile
+        __threadfence();
+      }
+      // this block writes the tile: sum of the 4 warps (whole tile) or of all blocks' partials in block order
+      if (!whole) {
+        // gather the partial sums into red[0] first: 16 bytes per thread and piece, four pieces in flight
+        float4* sum4 = reinterpret_cast<float4*>(red);
+        for (int id = tid; id < ROWS * X_ROWS / 4; id += CONSUMER_WARPS * 32) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int q0 = 0; q0 < pieces; q0 += 4) {
+            float4 t[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int cc = c_first + min(q0 + j, pieces - 1);
+              const int slot = (int)(unit_begin(cc, total, G) / kb) == tile ? 0 : 1;
+              t[j] = __ldcg(reinterpret_cast<const float4*>(p.scratch + ((size_t)cc * 2 + slot) * ROWS * X_ROWS) + id);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (q0 + j < pieces) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+          }
+          sum4[id] = v;
+        }
+        consumer_sync();
+      }
+      for (int id = tid; id < out_rows * X_ROWS; id += CONSUMER_WARPS * 32) {
+        const int m = id / out_rows, r = id - m * out_rows;
+        const int n = tile * out_rows + r;
+        if (m >= p.M || n >= p.N) continue;
+        auto value = [&](int row) -> float {
+          float v = 0.f;
+          if (whole) {
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * ROWS + row) * X_ROWS + m];
+          } else {
+            v = red[row * X_ROWS + m];
+          }
+          return __bfloat162float(__float2bfloat16_rn(v));
+        };
+        float v = value(r);
+        if (p.mode == 2) {
+          const float up = value(32 + r);
+          v = v / (1.0f + expf(-v)) * up;
+        }
+        if (p.mode == 1)
+          reinterpret_cast<float*>(p.y)[(size_t)m * p.ldc + n] = v;
+        else
+          reinterpret_cast<bf16*>(p.y)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v);
+      }
+      if (!whole && tid == 0) p.counters[tile] = 0;           // ready for the next launch
+      consumer_sync();
+    }
+  }
+}
+
+template <int NT, int STAGES>
+int launch(const Params& p, int grid, cudaStream_t stream) {
+  constexpr int X_ROWS = NT * 8;
+  constexpr size_t smem = 1024 + (size_t)STAGES * BOXES * (ROWS + X_ROWS) * 128 + (size_t)CONSUMER_WARPS * ROWS * X_ROWS * 4 +
+                          2 * STAGES * 8;
+  static bool attr_set = false;
+  if (!attr_set) {
+    NHV_CUDA(cudaFuncSetAttribute(gemm_stream_k_kernel<NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)smem), "gemm_stream_k");
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  NHV_CUDA(cudaLaunchKernelEx(&cfg, gemm_stream_k_kernel<NT, STAGES>, p), "gemm_stream_k");
+  return 0;
+}
+
+// ---------------------------------------------------------------- tensor maps (host)
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int row_stride_elems, int box_rows) {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
+    g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BOX_COLS, (cuuint32_t)box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapKey {
+  const void* base;
+  int rows, cols, box_rows;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.base) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols << 20) ^ (size_t)k.box_rows;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_weight_maps;   // weights do not move: one map per matrix
+std::mutex g_maps_mutex;
+
+}  // namespace
+
+// How much scratch the kernel wants for a grid of `grid` blocks: floats of partial sums, ints of counters
+// (the counters must be zero before the first launch; the kernel leaves them zero).
+NHV_API int nhv_gemm_stream_k_scratch(int grid, int max_tiles, size_t* partial_floats, size_t* counter_ints) {
+  *partial_floats = (size_t)grid * 2 * ROWS * 16;
+  *counter_ints = (size_t)max_tiles;
+  return 0;
+}
+
+// Reads and clears the error word (0: no bounded wait ever ran out).  Synchronises the device.
+NHV_API int nhv_gemm_stream_k_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_error, &zero, sizeof(int));
+  return v;
+}
+
+NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int N, int K, int lda, int ldc, int mode,
+                              int up_row_offset, float* scratch, int* counters, int counters_len, int grid,
+                              cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  NHV_REQUIRE(M > 0 && M <= 16, "gemm_stream_k: takes 1 to 16 tokens, got %d", M);
+  NHV_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && lda >= K && ldc >= N,
+              "gemm_stream_k: K and the row stride of x must be multiples of 8 (N=%d K=%d lda=%d)", N, K, lda);
+  NHV_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm_stream_k: x and W must be 16-byte aligned");
+  NHV_REQUIRE(mode >= 0 && mode <= 2 && grid > 0 && scratch && counters, "gemm_stream_k: bad arguments");
+  const int out_rows = mode == 2 ? ROWS / 2 : ROWS;
+  const int tiles = (N + out_rows - 1) / out_rows;
+  NHV_REQUIRE(tiles <= counters_len, "gemm_stream_k: %d tiles but room for %d counters", tiles, counters_len);
+  Params p;
+  p.y = y; p.x = (const bf16*)x; p.W = (const bf16*)W; p.scratch = scratch; p.counters = counters;
+  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset;
+  const int w_rows = mode == 2 ? up_row_offset + N : N, w_box = mode == 2 ? ROWS / 2 : ROWS;
+  {
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    const MapKey key{W, w_rows, K, w_box};
+    auto it = g_weight_maps.find(key);
+    if (it == g_weight_maps.end()) {
+      CUtensorMap m;
+      NHV_REQUIRE(make_map(&m, W, w_rows, K, K, w_box), "gemm_stream_k: cannot encode the tensor map of W [%d, %d]", w_rows, K);
+      it = g_weight_maps.emplace(key, m).first;
+    }
+    p.w_map = it->second;
+  }
+  NHV_REQUIRE(make_map(&p.x_map, x, M, K, lda, M <= 8 ? 8 : 16), "gemm_stream_k: cannot encode the tensor map of x [%d, %d]", M, K);
+  const long long total = (long long)tiles * ((K + BK - 1) / BK);
+  if (grid > total) grid = (int)total;
+  if (M <= 8) return launch<1, 5>(p, grid, stream);
+  return launch<2, 5>(p, grid, stream);
+}

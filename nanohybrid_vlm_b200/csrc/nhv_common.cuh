@@ -42,6 +42,35 @@ void nhv_set_error(const char* fmt, ...);
     }                                                                                 \
   } while (0)
 
+// Programmatic dependent launch.  Every kernel of this library is launched with the attribute that
+// lets it start while the kernel before it in the stream is still running, and every kernel begins
+// with pdl_prologue(): it lets the kernel after it start likewise, then waits until the kernel before
+// it has completed and its writes are visible.  Nothing may be read that another kernel writes, and
+// nothing written at all, before that wait; what a kernel does before it (fetching weights) overlaps
+// with its predecessor's tail.  Launch latency and pipeline fill leave the critical path this way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t nhv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

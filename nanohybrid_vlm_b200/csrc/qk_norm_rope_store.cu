@@ -26,6 +26,7 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, int qkv_str
                                           int n_tokens, int nq, int nkv, int d, int page_size, int n_pages,
                                           float eps, float weight_offset, int heads_per_token) {
   extern __shared__ float smem[];
+  pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long item = (long)blockIdx.x * QK_WARPS + warp;
   if (item >= (long)n_tokens * heads_per_token) return;
@@ -100,7 +101,7 @@ NHV_API int nhv_qk_norm_rope_store(int dtype, const void* qkv, int qkv_stride, v
   const int blocks = (int)((items + QK_WARPS - 1) / QK_WARPS);
   const size_t smem = (size_t)QK_WARPS * d * sizeof(float);
 #define LAUNCH(T)                                                                                              \
-  qk_norm_rope_store_kernel<T><<<blocks, QK_WARPS * 32, smem, stream>>>(                                       \
+  nhv_launch(qk_norm_rope_store_kernel<T>, blocks, QK_WARPS * 32, smem, stream,                                \
       (const T*)qkv, qkv_stride, (T*)q_out, q_out_stride, (T*)kv_pages, slot_mapping, positions, (const T*)q_w, \
       (const T*)k_w, cos_sin, rotary_dim, max_position, n_tokens, nq, nkv, d, page_size, n_pages, eps,        \
       weight_offset, heads_per_token)

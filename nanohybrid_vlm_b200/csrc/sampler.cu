@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(int* __restrict__ out, con
                                                       const int* __restrict__ positions, int vocab) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
+  pdl_prologue();
   const int row = blockIdx.x;
   const float* lg = logits + (size_t)row * ld;
   const float temp = temperatures[row];
@@ -82,7 +83,7 @@ NHV_API int nhv_sample(int* out, const float* logits, int ld, const float* tempe
   NHV_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab, "sample: bad sizes");
   int threads = 128;
   while (threads < 1024 && threads * 16 < vocab) threads <<= 1;
-  sample_kernel<<<n_rows, threads, 0, stream>>>(out, logits, ld, temperatures, seeds, positions, vocab);
+  nhv_launch(sample_kernel, n_rows, threads, 0, stream, out, logits, ld, temperatures, seeds, positions, vocab);
   NHV_CHECK_LAUNCH("sample");
   return 0;
 }

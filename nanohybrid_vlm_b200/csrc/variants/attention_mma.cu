@@ -9,13 +9,12 @@
 //    being (new token, query head of one KV head's group), token-major, so the grouped
 //    query heads share every key/value tile that is read; each of the 4 warps owns 16 rows
 //    and walks all keys up to its rows' positions.
-//  * single decoded tokens: a block owns one (request, KV head, split of 256 keys); the
-//    rows are the group's query heads, all 4 warps hold the same rows and take a quarter
-//    of every 64-key tile each; their partial (max, sum, output) are merged in shared
-//    memory and written to scratch; a second kernel merges the splits in ascending order.
+//  * single decoded tokens: the rows are the query heads of one KV head's group, all 4
+//    warps hold the same rows and take a quarter of every 64-key tile each; the tiles of all
+//    requests are dealt to a fixed grid of blocks in contiguous runs (see the decode kernel).
 //
 // Requests with one new token are left to the decode kernel, the others to the prefill
-// kernel, so a mixed batch is two launches plus the merge.  Keys and values of one layer:
+// kernel, so a mixed batch is two launches.  Keys and values of one layer:
 // [page][K|V][kv_head][slot][d] (bf16); a request's logical page p is block_table[p], -1
 // where a window has passed it.  Replaces the library calls at
 // nanovllm/layers/attention.py:67-74.
@@ -32,13 +31,16 @@ namespace {
 constexpr int D = NHV_ATTN_D;
 static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
 constexpr int CH = D / 8;          // 16-byte chunks in a row
-constexpr int ROW_CH = CH + 1;     // padded row stride in chunks: odd, so 8 rows of one chunk column hit 8 bank groups
+// ldmatrix reads one chunk column of 8 rows at a time: the 8 rows must fall into 8 different bank groups.
+// Rows of a multiple of 128 bytes swap chunks inside each group of 8 (chunk ^ (row & 7)); other head sizes
+// pad every row by one chunk, which makes the row stride odd.
+constexpr bool SWIZZLE = CH % 8 == 0;
+constexpr int ROW_CH = SWIZZLE ? CH : CH + 1;
 constexpr int BN = 64;             // keys per tile
 constexpr int TILE_ELEMS = BN * ROW_CH * 8;
 constexpr int KS = D / 16;         // k-steps of Q.K^T
 constexpr int DN = D / 8;          // n-tiles of P.V
 constexpr int THREADS = 128;
-constexpr int SPLIT = 256;         // keys per decode split
 constexpr float LOG2E = 1.4426950408889634f;
 
 typedef __nv_bfloat16 bf16;
@@ -71,7 +73,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // element offset of (row, 16-byte chunk) in a tile
-__device__ __forceinline__ int tile_off(int row, int chunk) { return (row * ROW_CH + chunk) * 8; }
+__device__ __forceinline__ int tile_off(int row, int chunk) {
+  return (row * ROW_CH + (SWIZZLE ? (chunk ^ (row & 7)) : chunk)) * 8;
+}
 
 struct PageGeom {
   const bf16* kv_pages;
@@ -80,8 +84,24 @@ struct PageGeom {
 };
 
 // Bring keys [key0, key0 + 64) of one request into a K tile and a V tile; keys outside [lo, hi) or on a
-// page that was given back are zero-filled.
-__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const PageGeom& g, int key0, int lo, int hi) {
+// page that was given back are zero-filled.  `page` >= -1: the whole tile lies on that page (page sizes that
+// are a multiple of the tile), looked up by the caller ahead of time; -2: look every row's page up here.
+__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const PageGeom& g, int key0, int lo, int hi, int page) {
+  const size_t v_off = (size_t)g.nkv * g.page_size * D;
+  if (page != -2) {
+    const bool page_ok = page >= 0 && page < g.n_pages;
+    const bf16* base = g.kv_pages + ((((size_t)(page_ok ? page : 0) * 2) * g.nkv + g.kvh) * g.page_size + (key0 % g.page_size)) * D;
+#pragma unroll 4
+    for (int id = threadIdx.x; id < BN * CH; id += THREADS) {
+      const int r = id / CH, c = id - r * CH;
+      const int j = key0 + r;
+      const bool ok = page_ok && j >= lo && j < hi;
+      const bf16* src = ok ? base + (size_t)r * D + c * 8 : g.kv_pages;
+      cp_async16(ks + tile_off(r, c), src, ok);
+      cp_async16(vs + tile_off(r, c), ok ? src + v_off : src, ok);
+    }
+    return;
+  }
   for (int id = threadIdx.x; id < BN * CH; id += THREADS) {
     const int r = id / CH, c = id - r * CH;
     const int j = key0 + r;
@@ -89,13 +109,19 @@ __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const PageGeom&
     const bf16* src = g.kv_pages;
     if (ok) {
       const int lp = j / g.page_size;
-      const int page = g.table[lp];
-      ok = page >= 0 && page < g.n_pages;
-      if (ok) src = g.kv_pages + ((((size_t)page * 2) * g.nkv + g.kvh) * g.page_size + (j - lp * g.page_size)) * D + c * 8;
+      const int pg = g.table[lp];
+      ok = pg >= 0 && pg < g.n_pages;
+      if (ok) src = g.kv_pages + ((((size_t)pg * 2) * g.nkv + g.kvh) * g.page_size + (j - lp * g.page_size)) * D + c * 8;
     }
     cp_async16(ks + tile_off(r, c), src, ok);
-    cp_async16(vs + tile_off(r, c), ok ? src + (size_t)g.nkv * g.page_size * D : src, ok);
+    cp_async16(vs + tile_off(r, c), ok ? src + v_off : src, ok);
   }
+}
+
+// The page of the tile that starts at key0, for the fast path of load_kv_tile; -2 if tiles may straddle pages.
+__device__ __forceinline__ int tile_page(const PageGeom& g, int key0, int hi) {
+  if (g.page_size % BN != 0) return -2;
+  return key0 < hi ? __ldg(g.table + key0 / g.page_size) : -1;
 }
 
 // Running softmax state of the two rows (lane/4 and lane/4 + 8) a thread holds of its warp's 16 rows.
@@ -205,6 +231,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);            // [2][tile]
   bf16* vbuf = kbuf + 2 * TILE_ELEMS;                        // [2][tile]
+  pdl_prologue();
   const int G = nq / nkv;
   const int kvh = blockIdx.y;
   int seq = -1, tile = blockIdx.x;
@@ -262,13 +289,16 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
   PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
   RowState st;
   init_state(st);
-  load_kv_tile(kbuf, vbuf, geom, key_begin, first_key, pos_hi + 1);
+  int page_next = tile_page(geom, key_begin + BN, pos_hi + 1);
+  load_kv_tile(kbuf, vbuf, geom, key_begin, first_key, pos_hi + 1, tile_page(geom, key_begin, pos_hi + 1));
   cp_async_commit();
   for (int it = 0; it < n_tiles; ++it) {
     const int stage = it & 1;
     if (it + 1 < n_tiles) {
+      const int page = page_next;
+      page_next = tile_page(geom, key_begin + (it + 2) * BN, pos_hi + 1);     // looked up one tile ahead
       load_kv_tile(kbuf + (stage ^ 1) * TILE_ELEMS, vbuf + (stage ^ 1) * TILE_ELEMS, geom, key_begin + (it + 1) * BN,
-                   first_key, pos_hi + 1);
+                   first_key, pos_hi + 1, page);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -297,143 +327,248 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
 }
 
 // ------------------------------------------------------------------------------------------------ decode
-// scratch per (request, query head, split): D floats of unnormalised output, then (max, sum) in part_ml.
-__global__ void __launch_bounds__(THREADS) attn_decode_split_kernel(
-    const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kv_pages, const int* __restrict__ block_table,
-    int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len, float* __restrict__ part_o,
-    float* __restrict__ part_ml, int nq, int nkv, int page_size, int n_pages, int window, float scale_log2,
-    int max_splits) {
+// Single decoded tokens, stream-K: the work is the flat list of 64-key tiles of every (request with one new
+// token, block of up to 16 query heads of one KV head), request-major.  The grid is a fixed number of blocks
+// (a few per SM); block c owns the contiguous tiles [c * T / G, (c + 1) * T / G), so every block reads the
+// same number of keys whatever the batch looks like, and a short batch spreads over as many blocks as it has
+// tiles.  A block walks its range piece by piece (a piece: its tiles of one (request, head block)).  If a
+// piece is the whole of its (request, head block) the block writes the output; otherwise it stores (max,
+// sum, unnormalised output) to scratch, and the block that arrives last at that (request, head block)'s
+// counter merges all pieces in block order and writes the output.  No block waits for another.
+constexpr int MAX_DECODE_SEQS = 512;
+constexpr int MIN_TILES = 4;
+#ifndef NHV_ATTN_DECODE_STAGES
+#define NHV_ATTN_DECODE_STAGES 2
+#endif
+constexpr int DSTAGES = NHV_ATTN_DECODE_STAGES;              // key/value tiles in the decode kernel's ring
+constexpr int Q_ELEMS = 16 * ROW_CH * 8;
+
+__device__ __forceinline__ int tile_owner(long long u, long long total, int G) { return (int)(((u + 1) * G - 1) / total); }
+
+__global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1) attn_decode_kernel(
+    const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride, const bf16* __restrict__ kv_pages,
+    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int n_seqs, int nq, int nkv,
+    int page_size, int n_pages, int window, float scale_log2, int max_pieces) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);
-  bf16* vbuf = kbuf + 2 * TILE_ELEMS;
+  bf16* vbuf = kbuf + DSTAGES * TILE_ELEMS;
+  bf16* qbuf = vbuf + DSTAGES * TILE_ELEMS;                   // [16 rows][padded d]
+  __shared__ unsigned short s_cnt[MAX_DECODE_SEQS];          // tiles of each request (0: not a single-token request)
+  __shared__ int s_prefix[MAX_DECODE_SEQS + 1];
+  __shared__ int s_flag;
+  pdl_prologue();
   const int G = nq / nkv;
-  const int heads_per_block = min(G, 16);
-  const int chunks = (G + 15) / 16;                          // groups of more than 16 heads take several blocks
-  const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y - kvh * chunks) * 16;
-  const int gn = min(heads_per_block, G - g0);
-  const int seq = blockIdx.z, split = blockIdx.x;
-  if (cu_q[seq + 1] - cu_q[seq] != 1) return;
-  const int total = kv_len[seq];
-  const int lo = window > 0 ? max(0, total - window) : 0;
-  const int k0 = max(split * SPLIT, lo), k1 = min(total, (split + 1) * SPLIT);
-  if (k0 >= k1) return;
+  const int rows_per = min(G, 16);
+  const int chunks = (G + 15) / 16;                          // groups of more than 16 heads: several head blocks
+  const int H = nkv * chunks;                                // head blocks per request
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const size_t tok = cu_q[seq];
 
-  for (int id = threadIdx.x; id < 16 * CH; id += THREADS) {
-    const int R = id / CH, c = id - R * CH;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (R < gn) v = *reinterpret_cast<const uint4*>(q + tok * q_stride + (size_t)(kvh * G + g0 + R) * D + c * 8);
-    *reinterpret_cast<uint4*>(kbuf + tile_off(R, c)) = v;
+  for (int sq = threadIdx.x; sq < n_seqs; sq += THREADS) {
+    int nt = 0;
+    if (cu_q[sq + 1] - cu_q[sq] == 1) {
+      const int total = kv_len[sq];
+      const int lo = window > 0 ? max(0, total - window) : 0;
+      nt = (total - 1) / BN - lo / BN + 1;
+    }
+    s_cnt[sq] = (unsigned short)min(nt, 65535);
   }
   __syncthreads();
-  uint32_t qf[KS][4];
-  load_q_frags(qf, kbuf, 0);
-  __syncthreads();
-
-  int row_lo[2], row_hi[2];
+  if (warp == 0) {                                           // prefix sums: each lane a run of requests, then a warp scan
+    const int per = (n_seqs + 31) / 32;
+    const int b0 = min(lane * per, n_seqs), b1 = min(b0 + per, n_seqs);
+    int sum = 0;
+    for (int i = b0; i < b1; ++i) sum += s_cnt[i];
+    int incl = sum;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int R = (lane >> 2) + 8 * i;
-    row_lo[i] = k0;
-    row_hi[i] = R < gn ? k1 - 1 : -1;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - sum;
+    for (int i = b0; i < b1; ++i) { s_prefix[i] = run; run += s_cnt[i]; }
+    if (lane == 31) s_prefix[n_seqs] = incl;
   }
-  const int key_begin = split * SPLIT;
-  const int n_tiles = (k1 - 1 - key_begin) / BN + 1;
-  PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
-  RowState st;
-  init_state(st);
-  load_kv_tile(kbuf, vbuf, geom, key_begin, k0, k1);
-  cp_async_commit();
-  for (int it = 0; it < n_tiles; ++it) {
-    const int stage = it & 1;
-    if (it + 1 < n_tiles) {
-      load_kv_tile(kbuf + (stage ^ 1) * TILE_ELEMS, vbuf + (stage ^ 1) * TILE_ELEMS, geom, key_begin + (it + 1) * BN, k0, k1);
+  __syncthreads();
+  const long long T = (long long)H * s_prefix[n_seqs];
+  // at least MIN_TILES tiles per block (a short batch uses fewer blocks), so that every block has work, the
+  // owners of consecutive tiles are consecutive blocks and a request is cut into few pieces
+  const int NB = (int)max(1LL, min((long long)gridDim.x, T / MIN_TILES));
+  const int c = blockIdx.x;
+  if (c >= NB || T == 0) return;
+  const long long u0 = (long long)c * T / NB, u1 = (long long)(c + 1) * T / NB;
+
+  long long u = u0;
+  while (u < u1) {
+    // which request, head block and tile is u?
+    int lo_s = 0, hi_s = n_seqs;
+    while (lo_s < hi_s) {
+      const int mid = (lo_s + hi_s) >> 1;
+      if ((long long)H * s_prefix[mid + 1] > u) hi_s = mid; else lo_s = mid + 1;
+    }
+    const int seq = lo_s;
+    const int nt = s_cnt[seq];
+    const long long seq_base = (long long)H * s_prefix[seq];
+    const int hb = (int)((u - seq_base) / nt), t_begin = (int)((u - seq_base) - (long long)hb * nt);
+    const long long piece_first = seq_base + (long long)hb * nt;          // first tile of this (request, head block)
+    const int n_tiles = (int)(min(u1, piece_first + nt) - u);
+    const bool whole = t_begin == 0 && n_tiles == nt;
+    u += n_tiles;
+
+    const int kvh = hb / chunks, g0 = (hb - kvh * chunks) * 16;
+    const int gn = min(rows_per, G - g0);
+    const int total = kv_len[seq];
+    const int lo = window > 0 ? max(0, total - window) : 0;
+    const int key_begin = (lo / BN + t_begin) * BN;
+    const size_t tok = cu_q[seq];
+    PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
+
+    // the first tiles are on their way while q is staged
+#pragma unroll
+    for (int pre = 0; pre < DSTAGES - 1; ++pre) {
+      if (pre < n_tiles)
+        load_kv_tile(kbuf + pre * TILE_ELEMS, vbuf + pre * TILE_ELEMS, geom, key_begin + pre * BN, lo, total,
+                     tile_page(geom, key_begin + pre * BN, total));
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    }
+    int page_next = tile_page(geom, key_begin + (DSTAGES - 1) * BN, total);
+    for (int id = threadIdx.x; id < 16 * CH; id += THREADS) {
+      const int R = id / CH, cc = id - R * CH;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (R < gn) v = *reinterpret_cast<const uint4*>(q + tok * q_stride + (size_t)(kvh * G + g0 + R) * D + cc * 8);
+      *reinterpret_cast<uint4*>(qbuf + tile_off(R, cc)) = v;
     }
     __syncthreads();
-    const int key_base = key_begin + it * BN;
-    if (key_base + warp * 16 < k1 && key_base + warp * 16 + 16 > k0)
-      warp_tile<2>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, warp * 16, key_base, row_lo, row_hi, scale_log2);
+    uint32_t qf[KS][4];
+    load_q_frags(qf, qbuf, 0);
+    int row_lo[2], row_hi[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      row_lo[i] = lo;
+      row_hi[i] = (lane >> 2) + 8 * i < gn ? total - 1 : -1;
+    }
+    RowState st;
+    init_state(st);
+    for (int it = 0; it < n_tiles; ++it) {
+      const int stage = it % DSTAGES;
+      const int nxt = it + DSTAGES - 1;
+      if (nxt < n_tiles) {
+        const int page = page_next;
+        page_next = tile_page(geom, key_begin + (nxt + 1) * BN, total);          // looked up one tile ahead
+        load_kv_tile(kbuf + (nxt % DSTAGES) * TILE_ELEMS, vbuf + (nxt % DSTAGES) * TILE_ELEMS, geom, key_begin + nxt * BN,
+                     lo, total, page);
+      }
+      cp_async_commit();                                       // one group per iteration, empty or not
+      cp_async_wait<DSTAGES - 1>();
+      __syncthreads();
+      const int key_base = key_begin + it * BN;
+      if (key_base + warp * 16 < total && key_base + warp * 16 + 16 > lo)
+        warp_tile<2>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, warp * 16, key_base, row_lo, row_hi, scale_log2);
+      __syncthreads();
+    }
+    cp_async_wait<0>();
+    // merge the 4 warps (each saw a quarter of every tile) through shared memory
+    float* mo = reinterpret_cast<float*>(smem_raw);            // [4 warps][16 rows][D]
+    float* mml = mo + 4 * 16 * D;                              // [4][16][2]
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float l = st.l[i];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      const int R = (lane >> 2) + 8 * i;
+      float* dst = mo + ((size_t)warp * 16 + R) * D + ((lane & 3) << 1);
+#pragma unroll
+      for (int n = 0; n < DN; ++n) {
+        dst[n * 8] = st.o[n][2 * i];
+        dst[n * 8 + 1] = st.o[n][2 * i + 1];
+      }
+      if ((lane & 3) == 0) {
+        mml[(warp * 16 + R) * 2] = st.m[i];
+        mml[(warp * 16 + R) * 2 + 1] = l;
+      }
+    }
     __syncthreads();
-  }
-  // merge the 4 warps (each saw a quarter of every tile) through shared memory
-  float* mo = reinterpret_cast<float*>(smem_raw);            // [4 warps][16 rows][D]
-  float* mml = mo + 4 * 16 * D;                              // [4][16][2]
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    float l = st.l[i];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    const int R = (lane >> 2) + 8 * i;
-    float* dst = mo + ((size_t)warp * 16 + R) * D + ((lane & 3) << 1);
-#pragma unroll
-    for (int n = 0; n < DN; ++n) {
-      dst[n * 8] = st.o[n][2 * i];
-      dst[n * 8 + 1] = st.o[n][2 * i + 1];
+    const size_t unit = (size_t)seq * H + hb;                  // this (request, head block)
+    int pieces = 1, piece = 0;
+    if (!whole) {
+      const int first_owner = tile_owner(piece_first, T, NB);
+      pieces = tile_owner(piece_first + nt - 1, T, NB) - first_owner + 1;
+      piece = min(c - first_owner, max_pieces - 1);          // never beyond the scratch, whatever the caller passed
     }
-    if ((lane & 3) == 0) {
-      mml[(warp * 16 + R) * 2] = st.m[i];
-      mml[(warp * 16 + R) * 2 + 1] = l;
-    }
-  }
-  __syncthreads();
-  for (int id = threadIdx.x; id < gn * D; id += THREADS) {
-    const int R = id / D, c = id - R * D;
-    float M = -INFINITY;
+    float* po = part_o + (unit * max_pieces + piece) * rows_per * D;
+    float* pml = part_ml + (unit * max_pieces + piece) * rows_per * 2;
+    for (int id = threadIdx.x; id < gn * D; id += THREADS) {
+      const int R = id / D, cc = id - R * D;
+      float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + R) * 2]);
-    float acc = 0.f, L = 0.f;
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + R) * 2]);
+      float acc = 0.f, L = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = mml[(w * 16 + R) * 2];
-      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-      acc += mo[((size_t)w * 16 + R) * D + c] * f;
-      L += mml[(w * 16 + R) * 2 + 1] * f;
+      for (int w = 0; w < 4; ++w) {
+        const float mw = mml[(w * 16 + R) * 2];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+        acc += mo[((size_t)w * 16 + R) * D + cc] * f;
+        L += mml[(w * 16 + R) * 2 + 1] * f;
+      }
+      if (whole) {
+        out[tok * out_stride + (size_t)(kvh * G + g0 + R) * D + cc] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      } else {
+        po[R * D + cc] = acc;
+        if (cc == 0) { pml[R * 2] = M; pml[R * 2 + 1] = L; }
+      }
     }
-    const size_t slot = ((size_t)seq * nq + kvh * G + g0 + R) * max_splits + split;
-    part_o[slot * D + c] = acc;
-    if (c == 0) {
-      part_ml[slot * 2] = M;
-      part_ml[slot * 2 + 1] = L;
+    if (!whole) {
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) s_flag = atomicAdd(&counters[unit], 1);
+      __syncthreads();
+      if (s_flag == pieces - 1) {                              // the last piece to arrive: merge all, in piece order
+        __threadfence();
+        const float* bo = part_o + unit * max_pieces * rows_per * D;
+        const float* bml = part_ml + unit * max_pieces * rows_per * 2;
+        // the pieces' (max, sum) first: few numbers, loaded side by side into shared memory
+        float* sml = reinterpret_cast<float*>(smem_raw);       // [pieces][gn][2]
+        for (int id = threadIdx.x; id < pieces * gn * 2; id += THREADS) {
+          const int pc = id / (gn * 2), rem = id - pc * (gn * 2);
+          sml[id] = __ldcg(bml + (size_t)pc * rows_per * 2 + rem);
+        }
+        __syncthreads();
+        for (int id = threadIdx.x; id < gn * (D / 4); id += THREADS) {
+          const int R = id / (D / 4), c4 = id - R * (D / 4);
+          float M = -INFINITY;
+          for (int pc = 0; pc < pieces; ++pc) M = fmaxf(M, sml[(pc * gn + R) * 2]);
+          float L = 0.f;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int p0 = 0; p0 < pieces; p0 += 4) {             // four independent 16-byte loads in flight
+            float4 t[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              t[j] = __ldcg(reinterpret_cast<const float4*>(bo + ((size_t)min(p0 + j, pieces - 1) * rows_per + R) * D) + c4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (p0 + j >= pieces) break;
+              const float m = sml[((p0 + j) * gn + R) * 2];
+              if (m == -INFINITY) continue;
+              const float f = exp2f(m - M);
+              acc.x += t[j].x * f; acc.y += t[j].y * f; acc.z += t[j].z * f; acc.w += t[j].w * f;
+              L += sml[((p0 + j) * gn + R) * 2 + 1] * f;
+            }
+          }
+          const float inv = L > 0.f ? 1.0f / L : 0.f;
+          bf16* dst = out + tok * out_stride + (size_t)(kvh * G + g0 + R) * D + c4 * 4;
+          *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+        }
+        if (threadIdx.x == 0) counters[unit] = 0;              // ready for the next launch
+      }
     }
+    __syncthreads();                                           // the tile buffers are reused by the next piece
   }
 }
 
-// Merge the splits of every (request with one new token, query head), in ascending order of split.
-__global__ void attn_decode_merge_kernel(bf16* __restrict__ out, int out_stride, const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml, const int* __restrict__ cu_q,
-                                         const int* __restrict__ kv_len, int nq, int window, int max_splits) {
-  const int seq = blockIdx.y, head = blockIdx.x;
-  if (cu_q[seq + 1] - cu_q[seq] != 1) return;
-  const int total = kv_len[seq];
-  const int lo = window > 0 ? max(0, total - window) : 0;
-  const int s_first = lo / SPLIT, s_last = (total - 1) / SPLIT;
-  const size_t base = ((size_t)seq * nq + head) * max_splits;
-  float M = -INFINITY;
-  for (int s = s_first; s <= s_last; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float L = 0.f;
-  for (int s = s_first; s <= s_last; ++s) {
-    const float m = part_ml[(base + s) * 2];
-    L += m == -INFINITY ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(m - M);
-  }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
-  bf16* dst = out + (size_t)cu_q[seq] * out_stride + (size_t)head * D;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
-    float acc = 0.f;
-    for (int s = s_first; s <= s_last; ++s) {
-      const float m = part_ml[(base + s) * 2];
-      if (m != -INFINITY) acc += part_o[(base + s) * D + c] * exp2f(m - M);
-    }
-    dst[c] = __float2bfloat16_rn(acc * inv);
-  }
-}
-
-constexpr size_t kSmemBytes = (size_t)4 * TILE_ELEMS * sizeof(bf16);
-static_assert(kSmemBytes >= (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float), "merge buffer must fit the tile buffers");
+constexpr size_t kSmemBytes = (size_t)4 * TILE_ELEMS * sizeof(bf16);                         // prefill: two K and two V tiles
+constexpr size_t kDecodeSmemBytes = (size_t)(2 * DSTAGES * TILE_ELEMS + Q_ELEMS) * sizeof(bf16);
+static_assert((size_t)4 * TILE_ELEMS * sizeof(bf16) >= (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float),
+              "merge buffer must fit the tile buffers");
 
 }  // namespace
 
@@ -451,26 +586,31 @@ static char g_err[384] = "";
   } while (0)
 
 NHV_API const char* NHV_FN(nhv_attn_mma_last_error_d)() { return g_err; }
-NHV_API int NHV_FN(nhv_attn_mma_split_d)() { return SPLIT; }
+NHV_API int NHV_FN(nhv_attn_mma_tile_d)() { return BN; }
 
-// The step's attention in bfloat16: prompt portions, then single tokens (split and merge).
-// n_prefill_tokens / n_decode_seqs: how many of the step's tokens / requests are of each kind (0 skips
-// that launch).  scratch_o: [n_seqs * nq * max_splits * D] floats, scratch_ml: [n_seqs * nq * max_splits * 2].
+// The step's attention in bfloat16: prompt portions, then single tokens.
+// n_prefill_tokens / n_decode_seqs: how many of the step's tokens / requests are of each kind (0 skips that
+// launch).  Decoding needs scratch: scratch_o [n_seqs * head_blocks * max_pieces * rows * D] floats, scratch_ml
+// [... * rows * 2] floats and counters [n_seqs * head_blocks] ints that are zero (the kernel leaves them zero),
+// with head_blocks = nkv * ceil(group / 16), rows = min(group, 16), max_pieces >= ceil(longest context / 64) + 1.
+// decode_blocks: the grid of the decode kernel (a few blocks per SM).
 NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
                                    const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
                                    int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
                                    int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
-                                   float* scratch_ml, int max_splits, cudaStream_t stream) {
+                                   float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
+                                   cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   ATT_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
-  ATT_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)kv_pages % 16) == 0,
-              "attention: q and the pages must be 16-byte aligned");
+  ATT_REQUIRE(q_stride % 8 == 0 && out_stride % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)kv_pages % 16) == 0 &&
+                  ((uintptr_t)out % 8) == 0,
+              "attention: q and the pages must be 16-byte aligned, the output 8-byte aligned");
   const int G = nq / nkv;
   const float scale_log2 = scale * LOG2E;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) {
+        cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDecodeSmemBytes) != cudaSuccess) {
       snprintf(g_err, sizeof(g_err), "attention: cannot reserve %zu bytes of shared memory", kSmemBytes);
       return 2;
     }
@@ -481,19 +621,28 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
     const int tokens_per_block = BN / G;
     const int max_tiles = n_prefill_tokens / tokens_per_block + n_prefill_seqs;
     dim3 grid(max_tiles, nkv);
-    attn_prefill_kernel<<<grid, THREADS, kSmemBytes, stream>>>(
+    nhv_launch(attn_prefill_kernel, grid, THREADS, kSmemBytes, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
         n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block);
   }
   if (n_decode_seqs > 0) {
-    ATT_REQUIRE(scratch_o && scratch_ml && max_splits > 0, "attention: decoding needs scratch memory for its splits");
-    dim3 grid(max_splits, nkv * ((G + 15) / 16), n_seqs);
-    attn_decode_split_kernel<<<grid, THREADS, kSmemBytes, stream>>>(
-        (const bf16*)q, q_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len, scratch_o, scratch_ml, nq,
-        nkv, page_size, n_pages, window, scale_log2, max_splits);
-    dim3 mgrid(nq, n_seqs);
-    attn_decode_merge_kernel<<<mgrid, D < 128 ? 32 * ((D + 31) / 32) : 128, 0, stream>>>(
-        (bf16*)out, out_stride, scratch_o, scratch_ml, cu_q, kv_len, nq, window, max_splits);
+    ATT_REQUIRE(scratch_o && scratch_ml && counters && max_pieces > 0 && decode_blocks > 0,
+                "attention: decoding needs scratch memory for the pieces of split requests");
+    ATT_REQUIRE(n_seqs <= MAX_DECODE_SEQS, "attention: %d requests in a step, the decode kernel plans for up to %d",
+                n_seqs, MAX_DECODE_SEQS);
+    static int resident = 0;                                   // blocks of the decode kernel that fit the device at once
+    if (resident == 0) {
+      int per_sm = 0, dev = 0, sms = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel, THREADS, kDecodeSmemBytes) != cudaSuccess || per_sm < 1)
+        per_sm = 1;
+      resident = per_sm * sms;
+    }
+    decode_blocks = resident;
+    nhv_launch(attn_decode_kernel, dim3(decode_blocks), THREADS, kDecodeSmemBytes, stream,
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
+        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, max_pieces);
   }
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {

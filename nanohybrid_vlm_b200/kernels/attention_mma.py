@@ -21,16 +21,16 @@ def supports(head_dim: int, nq: int, nkv: int) -> bool:
 
 
 def get(head_dim: int):
-    """(launch function, keys per decode split) for this head size."""
+    """(launch function, keys per tile) for this head size."""
     if head_dim not in _libs:
         from ..csrc.build import ensure_variant
         lib = ctypes.CDLL(ensure_variant("attention_mma.cu", {"NHV_ATTN_D": head_dim}))
         fn = getattr(lib, f"nhv_attn_mma_d{head_dim}")
-        fn.argtypes = [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, P, P, I, P]
+        fn.argtypes = [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, P, P, P, I, I, P]
         fn.restype = c_int
         err = getattr(lib, f"nhv_attn_mma_last_error_d{head_dim}")
         err.restype = ctypes.c_char_p
-        split = getattr(lib, f"nhv_attn_mma_split_d{head_dim}")
+        split = getattr(lib, f"nhv_attn_mma_tile_d{head_dim}")
         split.restype = c_int
 
         def launch(*args, _fn=fn, _err=err):

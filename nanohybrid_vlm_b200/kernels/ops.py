@@ -150,18 +150,42 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     n_pages, two, h, page_size, d = kv_pages.shape
     assert two == 2 and h == nkv and d == head_dim
     assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
-    launch, split = attention_mma.get(head_dim)
-    scratch_o = scratch_ml = None
-    max_splits = 0
+    launch, tile = attention_mma.get(head_dim)
+    scratch_o = scratch_ml = counters = None
+    max_pieces = blocks = 0
     if n_decode_seqs > 0:
-        max_splits = -(-max_kv_len // split)
-        scratch_o = torch.empty(n_seqs * nq * max_splits * head_dim, dtype=torch.float32, device=q.device)
-        scratch_ml = torch.empty(n_seqs * nq * max_splits * 2, dtype=torch.float32, device=q.device)
+        # scratch for requests whose tiles are shared between blocks: one partial result per piece, and a
+        # zeroed arrival counter per (request, head block) that the kernel leaves zeroed
+        group = nq // nkv
+        rows, head_blocks = min(group, 16), nkv * -(-group // 16)
+        max_pieces = -(-max_kv_len // tile) + 1
+        blocks = 3 * _sm_count(q.device)
+        scratch_o = torch.empty(n_seqs * head_blocks * max_pieces * rows * head_dim, dtype=torch.float32, device=q.device)
+        scratch_ml = torch.empty(n_seqs * head_blocks * max_pieces * rows * 2, dtype=torch.float32, device=q.device)
+        counters = _decode_counters(q.device, n_seqs * head_blocks)
     library.LAUNCHES += 1
     launch(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
            block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
            n_decode_seqs, nq, nkv, page_size, n_pages, int(window), float(scale), _ptr(scratch_o), _ptr(scratch_ml),
-           max_splits, stream_ptr())
+           _ptr(counters), max_pieces, blocks, stream_ptr())
+
+
+_sm_counts: dict = {}
+_counter_buffers: dict = {}
+
+
+def _sm_count(device) -> int:
+    if device not in _sm_counts:
+        _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_counts[device]
+
+
+def _decode_counters(device, n: int) -> torch.Tensor:
+    """Zeroed ints that outlive the step (the decode kernel returns them to zero)."""
+    buf = _counter_buffers.get(device)
+    if buf is None or buf.numel() < n:
+        buf = _counter_buffers[device] = torch.zeros(max(n, 16384), dtype=torch.int32, device=device)
+    return buf
 
 
 def linear(out, x, weight) -> None:
@@ -177,8 +201,7 @@ def linear(out, x, weight) -> None:
         call("nhv_gemm_nt_simt", F32, out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K, N, 0,
              stream_ptr())
     elif small_m_ok(x, weight):
-        call("nhv_gemm_small_m", out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), N,
-             int(out.dtype == torch.float32), 0, stream_ptr())
+        _small_m(out, x, weight, M, N, K, int(out.dtype == torch.float32), 0)
     elif out.dtype == torch.float32:
         # the product is rounded to bfloat16 and then widened, as the reference's head does
         # (nanovllm/layers/embed_head.py:61, nanovllm/layers/sampler.py:12)
@@ -207,9 +230,37 @@ def swiglu_first_half(act, x, gate_up_weight) -> bool:
     M, K = x.shape
     inter = gate_up_weight.shape[0] // 2
     assert act.shape == (M, inter) and act.dtype == torch.bfloat16 and gate_up_weight.shape[1] == K
-    call("nhv_gemm_small_m", act.data_ptr(), x.data_ptr(), gate_up_weight.data_ptr(), M, inter, K, x.stride(0), inter,
-         2, inter, stream_ptr())
+    _small_m(act, x, gate_up_weight, M, inter, K, 2, inter)
     return True
+
+
+_stream_k_state: dict = {}
+STREAM_K_COUNTERS = 8192
+
+
+def _small_m(out, x, weight, M: int, N: int, K: int, mode: int, up_row_offset: int) -> None:
+    """The weight-streaming product for up to 16 tokens: the persistent TMA kernel, one block per SM, with
+    its scratch (partial sums of tiles that two blocks share, and the tiles' arrival counters)."""
+    dev = x.device
+    st = _stream_k_state.get(dev)
+    if st is None:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        st = _stream_k_state[dev] = (sms, torch.zeros(sms * 2 * 64 * 16, dtype=torch.float32, device=dev),
+                                     torch.zeros(STREAM_K_COUNTERS, dtype=torch.int32, device=dev))
+    sms, scratch, counters = st
+    tiles = -(-N // (32 if mode == 2 else 64))
+    if tiles > STREAM_K_COUNTERS:
+        call("nhv_gemm_small_m", out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), N, mode,
+             up_row_offset, stream_ptr())
+        return
+    call("nhv_gemm_stream_k", out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), N, mode,
+         up_row_offset, scratch.data_ptr(), counters.data_ptr(), STREAM_K_COUNTERS, sms, stream_ptr())
+
+
+def stream_k_error() -> int:
+    """0 unless a bounded wait inside the streaming product ever ran out (synchronises the device)."""
+    from .library import load_library
+    return load_library().nhv_gemm_stream_k_error()
 
 
 def linear_simt(out, x, weight) -> None:
