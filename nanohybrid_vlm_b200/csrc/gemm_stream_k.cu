@@ -44,6 +44,18 @@ constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 __device__ int g_error = 0;
+#ifdef NHV_STREAM_K_TIMING
+__device__ unsigned long long g_times[8][256][6];   // [launch % 8][block][event]
+__device__ int g_launch_no = 0;
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define STAMP(slot, ev) do { if (lane == 0) g_times[(slot) & 7][blockIdx.x & 255][ev] = now_ns(); } while (0)
+#else
+#define STAMP(slot, ev) do {} while (0)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -93,7 +105,13 @@ __device__ __forceinline__ void give_up_delay() {
   for (int i = 0; i < 2000; ++i) __nanosleep(200);
 }
 
-constexpr int BK = 256;                  // columns per stage
+#ifndef NHV_STREAM_K_BK
+#define NHV_STREAM_K_BK 256
+#endif
+#ifndef NHV_STREAM_K_STAGES
+#define NHV_STREAM_K_STAGES 5
+#endif
+constexpr int BK = NHV_STREAM_K_BK;      // columns per stage
 constexpr int BOX_COLS = 64;             // columns per TMA box: 128 bytes, the widest the 128-byte swizzle takes
 constexpr int BOXES = BK / BOX_COLS;
 
@@ -112,7 +130,7 @@ __device__ __forceinline__ long long unit_begin(int c, long long total, int G) {
 __device__ __forceinline__ int unit_owner(long long u, long long total, int G) { return (int)(((u + 1) * G - 1) / total); }
 
 template <int NT, int STAGES>
-__global__ void __launch_bounds__(THREADS, 1) gemm_stream_k_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(THREADS, NHV_STREAM_K_BK <= 128 ? 2 : 1) gemm_stream_k_kernel(const __grid_constant__ Params p) {
   constexpr int X_ROWS = NT * 8;
   constexpr int W_BOX_BYTES = ROWS * 128, X_BOX_BYTES = X_ROWS * 128;
   constexpr int STAGE_BYTES = BOXES * (W_BOX_BYTES + X_BOX_BYTES);     // W boxes first, then x boxes
@@ -133,6 +151,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_k_kernel(const __grid_
   const long long total = (long long)tiles * kb;
   const long long u0 = unit_begin(c, total, G), u1 = unit_begin(c + 1, total, G);
 
+#ifdef NHV_STREAM_K_TIMING
+  const int t_slot = p.lda >> 20;      // experiments pass the launch number in the high bits of lda
+#else
+  const int t_slot = 0;
+#endif
+  (void)t_slot;
+  if (warp == 0) STAMP(t_slot, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -174,7 +199,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_k_kernel(const __grid_
       // Fill the ring with weights while the kernel before this one may still be running, then wait for it.
       const int pre = (int)min((long long)STAGES, n_units);
       for (int i = 0; i < pre; ++i) issue_w(i);
+      STAMP(t_slot, 1);
       grid_dependency_wait();
+      STAMP(t_slot, 2);
       for (int i = 0; i < pre; ++i) issue_x(i);
       bool ok = true;
       for (long long i = STAGES; i < n_units; ++i) {
@@ -199,8 +226,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_k_kernel(const __grid_
         for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
     };
     clear();
-    constexpr int KSTEPS = BK / 16 / CONSUMER_WARPS;        // k-steps per warp per stage: one box per warp
-    static_assert(KSTEPS * 16 == BOX_COLS, "each consumer warp takes one box of a stage");
+    constexpr int KSTEPS = BK / 16 / CONSUMER_WARPS;        // k-steps per warp per stage
+    static_assert(KSTEPS >= 1 && BOX_COLS % (KSTEPS * 16) == 0, "a warp's columns of a stage lie inside one box");
     bool ok = true;
     for (long long u = u0; u < u1 && ok; ++u) {
       const long long i = u - u0;
@@ -208,12 +235,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_k_kernel(const __grid_
       const int tile = (int)(u / kb), k = (int)(u - (long long)tile * kb);
       ok = mbar_wait(&full[s], (uint32_t)(i / STAGES) & 1, 2);
       if (!ok) { give_up_delay(); break; }
+      if (warp == 0 && i == 0) STAMP(t_slot, 3);
+      if (warp == 0 && u == u1 - 1) STAMP(t_slot, 4);
       // this warp's box of the stage; inside a box row r holds its 16-byte chunk c at chunk (c ^ (r & 7))
-      const unsigned char* ws = ring + (size_t)s * STAGE_BYTES + warp * W_BOX_BYTES;
-      const unsigned char* xs = ring + (size_t)s * STAGE_BYTES + BOXES * W_BOX_BYTES + warp * X_BOX_BYTES;
+      const int my_box = warp * KSTEPS * 16 / BOX_COLS;
+      const unsigned char* ws = ring + (size_t)s * STAGE_BYTES + my_box * W_BOX_BYTES;
+      const unsigned char* xs = ring + (size_t)s * STAGE_BYTES + BOXES * W_BOX_BYTES + my_box * X_BOX_BYTES;
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk) {
-        const int c0 = kk * 2;
+        const int c0 = ((warp * KSTEPS + kk) * 2) % (BOX_COLS / 8);
         uint32_t b[4];
         {
           const int r = NT == 1 ? (lane & 7) : (lane & 7) + ((lane >> 4) << 3);
@@ -321,6 +351,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_k_kernel(const __grid_
       if (!whole && tid == 0) p.counters[tile] = 0;           // ready for the next launch
       consumer_sync();
     }
+    if (warp == 0) STAMP(t_slot, 5);
   }
 }
 
@@ -403,6 +434,10 @@ NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int 
                               int up_row_offset, float* scratch, int* counters, int counters_len, int grid,
                               cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+#ifdef NHV_STREAM_K_TIMING
+  const int timing_slot = lda >> 20;
+  lda &= (1 << 20) - 1;
+#endif
   NHV_REQUIRE(M > 0 && M <= 16, "gemm_stream_k: takes 1 to 16 tokens, got %d", M);
   NHV_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && lda >= K && ldc >= N,
               "gemm_stream_k: K and the row stride of x must be multiples of 8 (N=%d K=%d lda=%d)", N, K, lda);
@@ -414,6 +449,9 @@ NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int 
   Params p;
   p.y = y; p.x = (const bf16*)x; p.W = (const bf16*)W; p.scratch = scratch; p.counters = counters;
   p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset;
+#ifdef NHV_STREAM_K_TIMING
+  p.lda = lda | (timing_slot << 20);
+#endif
   const int w_rows = mode == 2 ? up_row_offset + N : N, w_box = mode == 2 ? ROWS / 2 : ROWS;
   {
     std::lock_guard<std::mutex> lock(g_maps_mutex);
@@ -429,6 +467,6 @@ NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int 
   NHV_REQUIRE(make_map(&p.x_map, x, M, K, lda, M <= 8 ? 8 : 16), "gemm_stream_k: cannot encode the tensor map of x [%d, %d]", M, K);
   const long long total = (long long)tiles * ((K + BK - 1) / BK);
   if (grid > total) grid = (int)total;
-  if (M <= 8) return launch<1, 5>(p, grid, stream);
-  return launch<2, 5>(p, grid, stream);
+  if (M <= 8) return launch<1, NHV_STREAM_K_STAGES>(p, grid, stream);
+  return launch<2, NHV_STREAM_K_STAGES>(p, grid, stream);
 }
