@@ -274,8 +274,148 @@ def bench_ours(args) -> dict:
     }
 
 
+def _unavailable(reason: str) -> dict:
+    return {"impl": "reference", "unavailable": " ".join(str(reason).split())[:300]}
+
+
+def _write_reference_model(folder: str, cfg: dict) -> None:
+    """A model folder the reference can open: config.json, a stand-in tokenizer (one word per token id; the
+    reference's engine insists on one, nanovllm/inputs.py:186-193) and safetensors shards with the same
+    kind of random weights as the other arm, written layer by layer."""
+    import torch
+    from safetensors.torch import save_file
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from nanohybrid_vlm_b200.weights.random_init import tensor_seed
+
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(dict(cfg, eos_token_id=0, bos_token_id=0), f)
+    vocab = {f"t{i}": i for i in range(cfg["vocab_size"])}
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="t0"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="t0", unk_token="t0").save_pretrained(folder)
+
+    H, nq, nkv, d, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                           cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
+
+    def draw(name, shape, norm=False):
+        gen = torch.Generator(device="cuda").manual_seed(tensor_seed(SEED, name))
+        t = torch.empty(shape, dtype=torch.float32, device="cuda").normal_(0.0, 0.01 if norm else 0.02, generator=gen)
+        return ((1.0 + t) if norm else t).to(torch.bfloat16).cpu()
+
+    shard = {n: draw(n, s) for n, s in (("model.embed_tokens.weight", (V, H)), ("lm_head.weight", (V, H)))}
+    shard["model.norm.weight"] = draw("model.norm.weight", (H,), norm=True)
+    save_file(shard, os.path.join(folder, "model-head.safetensors"))
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        shard = {}
+        for n, s in (("self_attn.q_proj.weight", (nq * d, H)), ("self_attn.k_proj.weight", (nkv * d, H)),
+                     ("self_attn.v_proj.weight", (nkv * d, H)), ("self_attn.o_proj.weight", (H, nq * d)),
+                     ("mlp.gate_proj.weight", (I, H)), ("mlp.up_proj.weight", (I, H)), ("mlp.down_proj.weight", (H, I))):
+            shard[p + n] = draw(p + n, s)
+        for n, s in (("input_layernorm.weight", (H,)), ("post_attention_layernorm.weight", (H,)),
+                     ("self_attn.q_norm.weight", (d,)), ("self_attn.k_norm.weight", (d,))):
+            shard[p + n] = draw(p + n, s, norm=True)
+        save_file(shard, os.path.join(folder, f"model-layer-{i:03d}.safetensors"))
+
+
 def bench_reference(args) -> dict:
-    return {"impl": "reference", "unavailable": "the reference arm is not wired up yet"}
+    """The unmodified reference (installed under baseline/_ref) through its own public API:
+    LLM(path).add_request / step, the same model shape, prompts, batch and timing as the other arm."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "nanovllm")):
+        return _unavailable("baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref <reference>)")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return _unavailable("no CUDA device")
+        sys.path.insert(0, ref_root)
+        from nanovllm import LLM, SamplingParams
+    except Exception as e:  # noqa: BLE001
+        return _unavailable(f"the reference cannot be imported: {type(e).__name__}: {e}")
+    layers = args.layers
+    cfg = dict(CONFIG_8B, num_hidden_layers=layers)
+    gen = torch.Generator().manual_seed(SEED)
+
+    def prompts(n):
+        return [torch.randint(0, cfg["vocab_size"], (PROMPT_LEN,), generator=gen).tolist() for _ in range(n)]
+
+    folder = tempfile.mkdtemp(prefix="ref_model_")
+    try:
+        _write_reference_model(folder, cfg)
+        llm = LLM(folder, max_model_len=CONTEXT, max_num_seqs=max(args.batch, 64), kvcache_block_size=PAGE,
+                  enforce_eager=args.eager, gpu_memory_utilization=0.85)
+        sp = SamplingParams(temperature=0.0, max_tokens=CONTEXT - PROMPT_LEN, ignore_eos=True)
+
+        def decode(batch, steps, warmup):
+            for p in prompts(batch):
+                llm.add_request(p, sp)
+            while llm.scheduler.waiting:
+                llm.step()
+            for _ in range(warmup):
+                llm.step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            e0.record()
+            for _ in range(steps):
+                llm.step()
+            e1.record()
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - t0
+            for seq in list(llm.scheduler.running):       # drop the requests: their pages go back
+                llm.scheduler.block_manager.deallocate(seq)
+            llm.scheduler.running.clear()
+            return e0.elapsed_time(e1) / steps, batch * steps / wall
+
+        sampler = ClockSampler()
+        sampler.start()
+        ms, e2e_tps = decode(args.batch, args.steps, args.warmup)
+        clocks = sampler.stop()
+        points = {}
+        for b in (1, 64):
+            pms, _ = decode(b, max(4, args.steps // 2), 3)
+            points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        times = []
+        for it in range(5):
+            llm.add_request(prompts(1)[0], SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            llm.step()
+            torch.cuda.synchronize()
+            if it >= 3:
+                times.append((time.perf_counter() - t0) * 1e3)
+        pf_ms = sum(times) / len(times)
+    except Exception as e:  # noqa: BLE001
+        return _unavailable(f"the reference does not run here: {type(e).__name__}: {e}")
+    finally:
+        import shutil
+        shutil.rmtree(folder, ignore_errors=True)
+    pk = peaks()
+    nums = model_numbers(cfg, layers)
+    step_bytes = nums["weight_bytes"] + args.batch * (PROMPT_LEN + args.warmup + args.steps / 2) * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    return {
+        "metric": METRIC, "value": round(args.batch / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random weights N(0,0.02), seed 2)",
+        "impl": "reference",
+        "config": {"model": "Qwen3-8B-shaped", "layers": layers, "layers_full": FULL_LAYERS, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE,
+                   "parallelism": "single-gpu", "l2": "inputs_exceed_l2 (16 GB of weights per step, no flush)",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
+        "gpu_launches": None,
+        "prefill": {"value": round(PROMPT_LEN / pf_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
+                    "frac": round(prefill_flops(cfg, layers, PROMPT_LEN) / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "clocks": clocks,
+    }
 
 
 def main() -> int:
