@@ -470,3 +470,76 @@ NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int 
   if (M <= 8) return launch<1, NHV_STREAM_K_STAGES>(p, grid, stream);
   return launch<2, NHV_STREAM_K_STAGES>(p, grid, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// An entry point that allocates nothing (declared in nhv_no_alloc.h; it has no counterpart in the
+// reference).  Same product as nhv_gemm_stream_k, but the partial sums and tile counters live in a
+// fixed array inside this library instead of buffers the caller allocates.
+namespace {
+
+constexpr int STATIC_MAX_GRID = 160;                                   // blocks (one per SM) the array has room for
+constexpr int STATIC_MAX_TILES = 4096;                                 // output tiles it has counters for
+constexpr size_t STATIC_PARTIAL_BYTES = (size_t)STATIC_MAX_GRID * 2 * ROWS * 16 * sizeof(float);   // 1.25 MiB
+constexpr size_t STATIC_COUNTER_BYTES = (size_t)STATIC_MAX_TILES * sizeof(int);                    // 16 KiB
+constexpr int STATIC_MAX_DEVICES = 64;
+
+// Held by every GPU that loads this library, until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_PARTIAL_BYTES + STATIC_COUNTER_BYTES];
+
+struct StaticScratch {
+  unsigned char* base = nullptr;   // device address of g_static_scratch on this device
+  int sms = 0;
+};
+StaticScratch g_static[STATIC_MAX_DEVICES];
+std::mutex g_static_mutex;
+
+}  // namespace
+
+NHV_API int nhv_gemm_stream_k_no_alloc(void* y, const void* x, const void* W, int M, int N, int K, int lda, int ldc,
+                                       int mode, int up_row_offset, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  NHV_REQUIRE(M > 0 && M <= 16, "gemm_stream_k_no_alloc: takes 1 to 16 tokens, got %d", M);
+  NHV_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && lda >= K && ldc >= N,
+              "gemm_stream_k_no_alloc: K and the row stride of x must be multiples of 8 (N=%d K=%d lda=%d)", N, K, lda);
+  NHV_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm_stream_k_no_alloc: x and W must be 16-byte aligned");
+  NHV_REQUIRE(mode >= 0 && mode <= 2, "gemm_stream_k_no_alloc: unknown mode %d", mode);
+  const int out_rows = mode == 2 ? ROWS / 2 : ROWS;
+  const int tiles = (N + out_rows - 1) / out_rows;
+  NHV_REQUIRE(tiles <= STATIC_MAX_TILES, "gemm_stream_k_no_alloc: N=%d makes %d output tiles, the built-in scratch has "
+              "counters for %d (N up to %d)", N, tiles, STATIC_MAX_TILES, STATIC_MAX_TILES * out_rows);
+  int dev = 0;
+  NHV_CUDA(cudaGetDevice(&dev), "gemm_stream_k_no_alloc");
+  NHV_REQUIRE(dev >= 0 && dev < STATIC_MAX_DEVICES, "gemm_stream_k_no_alloc: device %d is beyond the %d this library tracks", dev,
+              STATIC_MAX_DEVICES);
+  StaticScratch* st = &g_static[dev];
+  if (st->base == nullptr) {
+    // Set-up, once per device, with that device current.  In host code the array's name only stands for the
+    // symbol; the address a kernel can use comes from cudaGetSymbolAddress.
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (st->base == nullptr) {
+      unsigned char* ptr = nullptr;
+      NHV_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch), "gemm_stream_k_no_alloc: address of the built-in scratch");
+      NHV_REQUIRE(ptr != nullptr, "gemm_stream_k_no_alloc: the built-in scratch has no device address");
+      int sms = 0;
+      NHV_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "gemm_stream_k_no_alloc");
+      // the counters must start at zero (the kernel returns them to zero after every call that completes)
+      NHV_CUDA(cudaMemsetAsync(ptr + STATIC_PARTIAL_BYTES, 0, STATIC_COUNTER_BYTES, stream), "gemm_stream_k_no_alloc");
+      st->sms = sms;
+      st->base = ptr;
+    }
+  }
+  int grid = st->sms < STATIC_MAX_GRID ? st->sms : STATIC_MAX_GRID;
+  Params p;
+  p.y = y; p.x = (const bf16*)x; p.W = (const bf16*)W;
+  p.scratch = reinterpret_cast<float*>(st->base);
+  p.counters = reinterpret_cast<int*>(st->base + STATIC_PARTIAL_BYTES);
+  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset;
+  const int w_rows = mode == 2 ? up_row_offset + N : N, w_box = mode == 2 ? ROWS / 2 : ROWS;
+  // both tensor maps are encoded on the stack: no cache, nothing allocated on the host either
+  NHV_REQUIRE(make_map(&p.w_map, W, w_rows, K, K, w_box), "gemm_stream_k_no_alloc: cannot encode the tensor map of W [%d, %d]", w_rows, K);
+  NHV_REQUIRE(make_map(&p.x_map, x, M, K, lda, M <= 8 ? 8 : 16), "gemm_stream_k_no_alloc: cannot encode the tensor map of x [%d, %d]", M, K);
+  const long long total = (long long)tiles * ((K + BK - 1) / BK);
+  if (grid > total) grid = (int)total;
+  if (M <= 8) return launch<1, NHV_STREAM_K_STAGES>(p, grid, stream);
+  return launch<2, NHV_STREAM_K_STAGES>(p, grid, stream);
+}
