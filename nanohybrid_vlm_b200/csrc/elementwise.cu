@@ -83,6 +83,70 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x, T* 
   }
 }
 
+// bfloat16 rows of up to 8,192 elements (a multiple of 8): 16-byte loads and stores, the row's fp32 sums kept
+// in registers between the statistics and the scaling, so every element is read once and written once.
+constexpr int RN_THREADS = 256;
+constexpr int RN_CHUNKS = 4;      // 16-byte chunks per thread
+
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_bf16x8_kernel(
+    __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+    const __nv_bfloat16* __restrict__ w, const int* __restrict__ rows, int width8, float eps, int write_residual,
+    float weight_offset) {
+  __shared__ float red[33];
+  pdl_prologue();
+  const int r = blockIdx.x;
+  const size_t src = (size_t)(rows ? rows[r] : r) * width8;
+  const uint4* x4 = reinterpret_cast<const uint4*>(x) + src;
+  uint4* res4 = residual ? reinterpret_cast<uint4*>(residual) + src : nullptr;
+  float s[RN_CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_CHUNKS; ++i) {
+    const int c = threadIdx.x + i * RN_THREADS;
+    if (c < width8) {
+      const uint4 xv = x4[c];
+      const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(&xv);
+      if (res4) {
+        const uint4 rv = res4[c];
+        const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&rv);
+        uint4 nv;
+        __nv_bfloat16* nb = reinterpret_cast<__nv_bfloat16*>(&nv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          s[i][k] = __bfloat162float(xb[k]) + __bfloat162float(rb[k]);
+          nb[k] = __float2bfloat16_rn(s[i][k]);
+        }
+        if (write_residual) res4[c] = nv;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s[i][k] = __bfloat162float(xb[k]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss = fmaf(s[i][k], s[i][k], ss);
+    }
+  }
+  const float total = block_sum(ss, red);
+  const float rstd = 1.0f / sqrtf(total / (float)(width8 * 8) + eps);
+  uint4* out4 = reinterpret_cast<uint4*>(out) + (size_t)r * width8;
+  const uint4* w4 = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int i = 0; i < RN_CHUNKS; ++i) {
+    const int c = threadIdx.x + i * RN_THREADS;
+    if (c < width8) {
+      const uint4 wv = w4[c];
+      const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(&wv);
+      uint4 ov;
+      __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float n = __bfloat162float(__float2bfloat16_rn(s[i][k] * rstd));
+        ob[k] = __float2bfloat16_rn(n * (__bfloat162float(wb[k]) + weight_offset));
+      }
+      out4[c] = ov;
+    }
+  }
+}
+
 NHV_API int nhv_rmsnorm(int dtype, void* out, const void* x, void* residual, const void* w, const int* rows,
                         int n_rows, int width, float eps, int write_residual, float weight_offset,
                         cudaStream_t stream) {
@@ -92,6 +156,13 @@ NHV_API int nhv_rmsnorm(int dtype, void* out, const void* x, void* residual, con
   NHV_REQUIRE(smem <= 200 * 1024, "rmsnorm: width %d is beyond the %d floats a row buffer holds", width,
               200 * 1024 / 4);
   NHV_REQUIRE(!(rows && residual && write_residual), "rmsnorm: a gathered norm cannot write the residual back");
+  if (dtype == NHV_BF16 && width % 8 == 0 && width <= RN_THREADS * RN_CHUNKS * 8 && ((uintptr_t)out % 16) == 0 &&
+      ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && (!residual || ((uintptr_t)residual % 16) == 0)) {
+    nhv_launch(rmsnorm_bf16x8_kernel, n_rows, RN_THREADS, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x,
+               (__nv_bfloat16*)residual, (const __nv_bfloat16*)w, rows, width / 8, eps, write_residual, weight_offset);
+    NHV_CHECK_LAUNCH("rmsnorm");
+    return 0;
+  }
   int threads = 32;
   while (threads < 1024 && threads * 4 < width) threads <<= 1;
 #define LAUNCH(T)                                                                                          \
