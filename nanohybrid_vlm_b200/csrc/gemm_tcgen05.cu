@@ -301,7 +301,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         pieces = unit_owner(t_last, total, G) - c_first + 1;
         const int slot = (int)(u0 / kb) == tile ? 0 : 1;
         float* mine = p.scratch + ((size_t)c * 2 + slot) * TILE_ROWS * NT;
-        for (int id = tid; id < TILE_ROWS * NT; id += EPI_THREADS) mine[id] = parked[(id / NT) * OUT_LD + (id % NT)];
+        for (int id = tid; id < TILE_ROWS * NT / 4; id += EPI_THREADS) {
+          const int e = id * 4;
+          const float* src = parked + (e / NT) * OUT_LD + (e % NT);
+          reinterpret_cast<float4*>(mine)[id] = make_float4(src[0], src[1], src[2], src[3]);
+        }
         __threadfence();
         epi_sync();
         if (tid == 0) s_flag = atomicAdd(&p.counters[tile], 1);
@@ -309,41 +313,61 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         finisher = s_flag == pieces - 1;
         if (finisher) {                                         // the last block to arrive: add all partials in block order
           __threadfence();
-          for (int id = tid; id < TILE_ROWS * NT / 4; id += EPI_THREADS) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          // four outputs of 16 bytes per thread at a time, each with up to four pieces in flight: the loads
+          // do not depend on one another, so the L2 latency is paid once per batch and not once per load
+          const float4* __restrict__ parts = reinterpret_cast<const float4*>(p.scratch);
+          constexpr int PIECE_F4 = TILE_ROWS * NT / 4;
+          for (int id0 = tid; id0 < PIECE_F4; id0 += 4 * EPI_THREADS) {
+            float4 acc[4];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int q0 = 0; q0 < pieces; q0 += 4) {
-              float4 t[4];
+              float4 t[4][4];
+              size_t base[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int cc = c_first + min(q0 + j, pieces - 1);
                 const int sl = (int)(unit_begin(cc, total, G) / kb) == tile ? 0 : 1;
-                t[j] = __ldcg(reinterpret_cast<const float4*>(p.scratch + ((size_t)cc * 2 + sl) * TILE_ROWS * NT) + id);
+                base[j] = ((size_t)cc * 2 + sl) * PIECE_F4;
               }
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                if (q0 + j < pieces) { acc.x += t[j].x; acc.y += t[j].y; acc.z += t[j].z; acc.w += t[j].w; }
+              for (int v = 0; v < 4; ++v)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) t[v][j] = __ldcg(parts + base[j] + min(id0 + v * EPI_THREADS, PIECE_F4 - 1));
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  if (q0 + j < pieces) { acc[v].x += t[v][j].x; acc[v].y += t[v][j].y; acc[v].z += t[v][j].z; acc[v].w += t[v][j].w; }
             }
-            const int e = id * 4;
-            float* dst = parked + (e / NT) * OUT_LD + (e % NT);
-            dst[0] = acc.x; dst[1] = acc.y; dst[2] = acc.z; dst[3] = acc.w;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int id = id0 + v * EPI_THREADS;
+              if (id < PIECE_F4) {
+                const int e = id * 4;
+                float* dst = parked + (e / NT) * OUT_LD + (e % NT);
+                dst[0] = acc[v].x; dst[1] = acc[v].y; dst[2] = acc[v].z; dst[3] = acc[v].w;
+              }
+            }
           }
           epi_sync();
         }
       }
       if (finisher) {
-        for (int id = tid; id < out_rows * NT; id += EPI_THREADS) {
-          const int m = id / out_rows, r = id - m * out_rows;
-          const int n = tile * out_rows + r;
-          if (m >= p.M || n >= p.N) continue;
-          float v = __bfloat162float(__float2bfloat16_rn(parked[r * OUT_LD + m]));
-          if (p.mode == 2) {
-            const float up = __bfloat162float(__float2bfloat16_rn(parked[(TILE_ROWS / 2 + r) * OUT_LD + m]));
-            v = v / (1.0f + expf(-v)) * up;
+        // thread = output column n (a weight row), loop over tokens: for one token the threads write one run of bytes
+        const int n = tile * out_rows + tid;
+        if (tid < out_rows && n < p.N) {
+          for (int m = 0; m < p.M; ++m) {
+            float v = __bfloat162float(__float2bfloat16_rn(parked[tid * OUT_LD + m]));
+            if (p.mode == 2) {
+              const float up = __bfloat162float(__float2bfloat16_rn(parked[(TILE_ROWS / 2 + tid) * OUT_LD + m]));
+              v = v / (1.0f + expf(-v)) * up;
+            }
+            if (p.mode == 1)
+              reinterpret_cast<float*>(p.y)[(size_t)m * p.ldc + n] = v;
+            else
+              reinterpret_cast<bf16*>(p.y)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v);
           }
-          if (p.mode == 1)
-            reinterpret_cast<float*>(p.y)[(size_t)m * p.ldc + n] = v;
-          else
-            reinterpret_cast<bf16*>(p.y)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v);
         }
         if (!whole && tid == 0) p.counters[tile] = 0;           // ready for the next launch
       }

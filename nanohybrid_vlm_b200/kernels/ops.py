@@ -257,6 +257,36 @@ def _small_m(out, x, weight, M: int, N: int, K: int, mode: int, up_row_offset: i
          up_row_offset, scratch.data_ptr(), counters.data_ptr(), STREAM_K_COUNTERS, sms, stream_ptr())
 
 
+_tcgen05_state: dict = {}
+
+
+def linear_tcgen05(out, x, weight, mode: int = 0, up_row_offset: int = 0) -> None:
+    """out = x @ weight^T for 1 to 128 tokens with tcgen05.mma and tensor-memory accumulators
+    (csrc/gemm_tcgen05.cu).  mode 0: out bfloat16; 1: out float32 through bfloat16; 2: weight = [gate; up] rows,
+    out = silu(gate) * up.  Not on the default path: at these sizes the library product is still faster (see
+    the kernel's entry in the design notes); it is kept tested and callable."""
+    _need_cuda(out, x, weight)
+    _contig("out", out); _contig("weight", weight)
+    assert x.dtype == weight.dtype == torch.bfloat16 and x.stride(1) == 1
+    M, K = x.shape
+    N = out.shape[1]
+    dev = x.device
+    st = _tcgen05_state.get(dev)
+    if st is None:
+        sms = _sm_count(dev)
+        st = _tcgen05_state[dev] = (sms, torch.zeros(sms * 2 * 128 * 128, dtype=torch.float32, device=dev),
+                                    torch.zeros(STREAM_K_COUNTERS, dtype=torch.int32, device=dev))
+    sms, scratch, counters = st
+    call("nhv_gemm_tcgen05", out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), N, mode, up_row_offset,
+         scratch.data_ptr(), counters.data_ptr(), STREAM_K_COUNTERS, sms, stream_ptr())
+
+
+def tcgen05_error() -> int:
+    """0 unless a bounded wait inside the tcgen05 product ever ran out (synchronises the device)."""
+    from .library import load_library
+    return load_library().nhv_gemm_tcgen05_error()
+
+
 def stream_k_error() -> int:
     """0 unless a bounded wait inside the streaming product ever ran out (synchronises the device)."""
     from .library import load_library

@@ -148,6 +148,35 @@ def test_gemm_small_m(ops, M, N, K):
         assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
 
 
+@pytest.mark.parametrize("M", [17, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(384, 96), (1000, 264), (4096, 4096), (4098, 520)])
+def test_gemm_tcgen05(ops, M, N, K):
+    """The tensor-memory product (tcgen05.mma, TMA operands, stream-K over the SMs): plain, with float32
+    output, and fused with the feed-forward's activation; shapes that split tiles between blocks and
+    shapes whose edges are padded by the copy engine."""
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    ref = (x.double() @ w.double().t()).float()
+    t = dict(rtol=2e-2, atol=2e-2 * ref.abs().max().item() / 4)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear_tcgen05(out, dev(x), dev(w))
+    torch.testing.assert_close(out.cpu().float(), ref, **t)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    ops.linear_tcgen05(out32, dev(x), dev(w), mode=1)
+    assert torch.equal(out32.cpu(), out.cpu().float())
+    if N % 2 == 0:
+        inter = N // 2
+        act = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.linear_tcgen05(act, dev(x), dev(w), mode=2, up_row_offset=inter)
+        gu = out.cpu().float()
+        want = (gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]).to(torch.bfloat16)
+        # the fused form cuts K between blocks at other places than the plain one, so gate and up may each
+        # differ by one bfloat16 step before the activation
+        torch.testing.assert_close(act.cpu().float(), want.float(), rtol=3e-2, atol=2e-2)
+    assert ops.tcgen05_error() == 0
+
+
 def make_pages(k, v, page_size, n_pages, rng, dtype):
     """Scatter one request's keys/values [T, nkv, d] over shuffled pages. Returns pages tensor and table."""
     T, nkv, d = k.shape
