@@ -303,3 +303,139 @@ def test_toy_architecture_with_a_state_mixer_registers_builds_and_steps(tmp_path
     finally:
         ARCHITECTURES.unregister("ToyStateLM")
         MIXERS.unregister("moving_average")
+
+
+# ------------------------------------------------------------------------------------------------ a windowed layer
+
+WINDOW = dict(architectures=["ToyWindowLM"], model_type="toy_window", hidden_size=64, vocab_size=120, window=11,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=96, rms_norm_eps=1e-6,
+              rope_theta=10000.0, max_position_embeddings=256, torch_dtype="float32")
+
+
+def register_window_toy():
+    from nanohybrid_vlm_b200.config import ModelConfig, register_architecture
+    from nanohybrid_vlm_b200.parts import LayerRun, LayerSpec, ModelSpec, PartUse, part
+
+    def parse(raw):
+        cfg = ModelConfig(architecture="ToyWindowLM", model_type=raw["model_type"], vocab_size=raw["vocab_size"],
+                          hidden_size=raw["hidden_size"], max_position_embeddings=raw["max_position_embeddings"],
+                          dtype=torch.float32, eos_token_id=None)
+        object.__setattr__(cfg, "raw", raw)
+        return cfg
+
+    def build(cfg):
+        raw = cfg.raw
+        H = raw["hidden_size"]
+        norm = part("rmsnorm", width=H, eps=raw["rms_norm_eps"])
+        ffn = part("swiglu", intermediate_size=raw["intermediate_size"])
+        rope = part("rope", theta=raw["rope_theta"], rotary_dim=raw["head_dim"], max_position=raw["max_position_embeddings"])
+
+        def attn(window):
+            return part("gqa_attention", num_heads=raw["num_attention_heads"], num_kv_heads=raw["num_key_value_heads"],
+                        head_dim=raw["head_dim"], qk_norm_eps=raw["rms_norm_eps"], position=rope, window=window)
+
+        def layer(i, mixer):
+            return LayerSpec(part("prenorm_residual"), PartUse(mixer, f"layers.{i}.attn."), PartUse(norm, f"layers.{i}.norm1."),
+                             PartUse(ffn, f"layers.{i}.ffn."), PartUse(norm, f"layers.{i}.norm2."))
+
+        # all keys, the last `window` keys, all keys: two cache groups with pages of their own
+        return ModelSpec(architecture="ToyWindowLM", hidden_size=H, vocab_size=raw["vocab_size"],
+                         max_position=raw["max_position_embeddings"],
+                         embedding=PartUse(part("token_embedding", vocab_size=raw["vocab_size"]), "embed."),
+                         layers=(layer(0, attn(None)), layer(1, attn(raw["window"])), layer(2, attn(None))),
+                         order=(LayerRun(0), LayerRun(1), LayerRun(2)),
+                         final_norm=PartUse(norm, "final_norm."),
+                         head=PartUse(part("lm_head", vocab_size=raw["vocab_size"], tied=True), "head."))
+
+    register_architecture("ToyWindowLM", model_types=("toy_window",), parse_config=parse, build_spec=build, replace=True)
+
+
+def window_plain_logits(w, tokens):
+    raw, T = WINDOW, len(tokens)
+    nq, nkv, d, eps = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], raw["rms_norm_eps"]
+    cos, sin = plain.rope_table(d, raw["max_position_embeddings"], raw["rope_theta"])
+    pos = torch.arange(T)
+    h = w["embed.weight"][torch.tensor(tokens)]
+    residual = None
+    for i, window in enumerate((None, raw["window"], None)):
+        p = f"layers.{i}."
+        if residual is None:
+            residual, x = h, plain.rms_norm(h, w[p + "norm1.weight"], eps)
+        else:
+            x, residual = plain.add_rms_norm(h, residual, w[p + "norm1.weight"], eps)
+        q = plain.linear(x, w[p + "attn.q_proj.weight"]).view(T, nq, d)
+        k = plain.linear(x, w[p + "attn.k_proj.weight"]).view(T, nkv, d)
+        v = plain.linear(x, w[p + "attn.v_proj.weight"]).view(T, nkv, d)
+        q = plain.apply_rope(plain.rms_norm(q, w[p + "attn.q_norm.weight"], eps), cos[pos], sin[pos])
+        k = plain.apply_rope(plain.rms_norm(k, w[p + "attn.k_norm.weight"], eps), cos[pos], sin[pos])
+        o = reference_window_attention(q, k, v, d ** -0.5, window)
+        a = plain.linear(o.reshape(T, nq * d), w[p + "attn.o_proj.weight"])
+        x, residual = plain.add_rms_norm(a, residual, w[p + "norm2.weight"], eps)
+        h = plain.swiglu_mlp(x, w, p + "ffn.")
+    x, _ = plain.add_rms_norm(h, residual, w["final_norm.weight"], eps)
+    return plain.linear(x, w["embed.weight"])
+
+
+def reference_window_attention(q, k, v, scale, window):
+    T, nq, d = q.shape
+    G = nq // k.shape[1]
+    out = torch.empty(T, nq, d)
+    for t in range(T):
+        lo = max(0, t - window + 1) if window else 0
+        for h in range(nq):
+            s = (k[lo:t + 1, h // G].float() @ q[t, h].float()) * scale
+            out[t, h] = torch.softmax(s, 0) @ v[lo:t + 1, h // G].float()
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_a_window_have_pages_of_their_own_and_give_them_back(tmp_path, dtype):
+    """Three attention layers, the middle one sees only the last 11 keys: its group releases pages while the
+    request runs, the freed pages go to another request at once, and the logits stay those of the plain model."""
+    from safetensors.torch import load_file
+    from nanohybrid_vlm_b200.config import ARCHITECTURES, Config
+    from nanohybrid_vlm_b200.engine import ModelRunner, StepItem
+    from nanohybrid_vlm_b200.weights import write_random_model
+    register_window_toy()
+    try:
+        d = write_random_model(str(tmp_path / "win"), WINDOW, seed=4)
+        w = load_file(f"{d}/model.safetensors")
+        runner = ModelRunner(Config(d, dtype=dtype, kvcache_block_size=4, num_kvcache_blocks=30, max_num_seqs=2,
+                                    max_num_batched_tokens=64, max_model_len=96, enforce_eager=True))
+        cache = runner.cache
+        assert [g.window for g in runner.layout.groups] == [None, 11] and runner.layout.run_group == [0, 1, 0]
+        rng = np.random.default_rng(1)
+        toks = {"a": rng.integers(0, 120, 70).tolist(), "b": rng.integers(0, 120, 37).tolist()}
+        ref = {r: window_plain_logits(w, t) for r, t in toks.items()}
+        got = {"a": [], "b": []}
+        at = {"a": 0, "b": 0}
+        cuts = {"a": [30, 1, 1, 17, 2, 19], "b": [0, 0, 9, 1, 26, 1]}
+        for step in range(6):
+            items = []
+            for r in ("a", "b"):
+                n = cuts[r][step]
+                if n == 0:
+                    continue
+                cache.allocate(r, at[r] + n)
+                items.append(StepItem(r, toks[r][at[r]:at[r] + n], at[r], list(range(n))))
+                at[r] += n
+            logits = runner.step(items).cpu()
+            k = 0
+            for it in items:
+                got[it.req_id].append(logits[k:k + len(it.tokens)])
+                k += len(it.tokens)
+                cache.release_behind_window(it.req_id, at[it.req_id])
+            cache.check()
+        # request a: 70 tokens computed, the windowed group keeps only the pages of keys 60..69
+        table = cache.block_table("a", 1)
+        assert table[:15] == [-1] * 15 and all(p >= 0 for p in table[15:])
+        assert all(p >= 0 for p in cache.block_table("a", 0))
+        assert cache.pools[1].num_used < cache.pools[0].num_used
+        for r in toks:
+            g = torch.cat(got[r])
+            if dtype == "float32":
+                torch.testing.assert_close(g, ref[r], rtol=1e-4, atol=2e-5)
+            else:
+                assert (g - ref[r]).abs().max() <= 0.06 * ref[r].std()
+    finally:
+        ARCHITECTURES.unregister("ToyWindowLM")
