@@ -11,10 +11,20 @@ still running.  One page id of a group indexes the pages of every run of that gr
 A request's logical page i holds tokens [i * page_size, (i + 1) * page_size).  Its table
 lists the physical page of every logical page, -1 where a window has passed and the page
 was given back.
+
+Prefix reuse (the reference's default for this architecture, nanovllm/engine/block_manager.py:102-108,
+696-749, 811-825): every full page gets a hash chained over the page's token ids and the hash of the page
+before it; a new request whose leading pages hash (and compare) equal to pages still in the pool shares
+them instead of computing them.  The last page of a request is never shared, so at least one token is
+always computed.  Reuse is only offered when every group keeps all keys and the model has no fixed-size
+state: a window or a state cannot be rebuilt from shared pages.
 """
 from __future__ import annotations
 
+import hashlib
 from dataclasses import dataclass, field
+
+import numpy as np
 
 from .page_pool import OutOfPages, PagePool, StateSlotAllocator
 
@@ -33,7 +43,8 @@ class _Request:
 
 
 class CacheManager:
-    def __init__(self, groups: list[GroupSpec], page_size: int, num_pages: int | list[int], num_state_slots: int = 0):
+    def __init__(self, groups: list[GroupSpec], page_size: int, num_pages: int | list[int], num_state_slots: int = 0,
+                 enable_prefix_cache: bool = False):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.groups = list(groups)
@@ -44,6 +55,111 @@ class CacheManager:
         self.pools = [PagePool(n) for n in counts]
         self.slots = StateSlotAllocator(num_state_slots) if num_state_slots > 0 else None
         self._requests: dict[object, _Request] = {}
+        if enable_prefix_cache and not self.prefix_cache_possible(self.groups, num_state_slots):
+            raise ValueError("prefix reuse needs groups that keep every key and a model without per-request state")
+        self.prefix_cache = enable_prefix_cache
+        # per group: hash -> page, and for every page that carries a hash: (hash, its token ids)
+        self._by_hash: list[dict[int, int]] = [{} for _ in self.groups]
+        self._page_info: list[dict[int, tuple[int, tuple]]] = [{} for _ in self.groups]
+        self.prefix_hits = 0            # pages shared instead of computed, over the manager's life
+
+    @staticmethod
+    def prefix_cache_possible(groups, num_state_slots: int) -> bool:
+        return num_state_slots == 0 and all(g.window is None for g in groups)
+
+    # ------------------------------------------------------------------ prefix reuse
+    @staticmethod
+    def _page_hash(prev: int, tokens) -> int:
+        h = hashlib.blake2b(digest_size=8)
+        h.update(int(prev).to_bytes(8, "little", signed=False))
+        h.update(np.asarray(tokens, dtype=np.int64).tobytes())
+        return int.from_bytes(h.digest(), "little")
+
+    def _probe(self, token_ids) -> list[list[int]]:
+        """Per group: the pages that hold the request's leading full pages already (never its last page)."""
+        ps = self.page_size
+        n_lookup = (-(-len(token_ids) // ps)) - 1
+        hits: list[list[int]] = [[] for _ in self.groups]
+        prev = 0
+        for i in range(max(0, n_lookup)):
+            chunk = tuple(token_ids[i * ps:(i + 1) * ps])
+            prev = self._page_hash(prev, chunk)
+            found = []
+            for g in range(len(self.groups)):
+                page = self._by_hash[g].get(prev)
+                if page is None or self._page_info[g].get(page, (None, None))[1] != chunk:
+                    found = None
+                    break
+                found.append(page)
+            if found is None:
+                break
+            for g, page in enumerate(found):
+                hits[g].append(page)
+        return hits
+
+    def can_admit(self, req_id, token_ids) -> bool:
+        """Room for a new request's tokens, counting the pages it can share."""
+        if not self.prefix_cache or req_id in self._requests:
+            return self.can_allocate(req_id, len(token_ids))
+        total = -(-len(token_ids) // self.page_size)
+        for g, pages in enumerate(self._probe(token_ids)):
+            from_free = sum(1 for p in pages if self.pools[g].is_free(p))
+            if total - len(pages) + from_free > self.pools[g].num_free:
+                return False
+        return True
+
+    def admit(self, req_id, token_ids) -> int:
+        """Pages for a new request's tokens; returns how many leading tokens are already in the cache
+        (a multiple of the page size; 0 without prefix reuse)."""
+        if not self.prefix_cache or req_id in self._requests:
+            self.allocate(req_id, len(token_ids))
+            return 0
+        if not self.can_admit(req_id, token_ids):
+            raise OutOfPages(f"request {req_id!r}: no room for {len(token_ids)} tokens "
+                             f"(free pages per group: {[p.num_free for p in self.pools]})")
+        hits = self._probe(token_ids)
+        req = self._requests[req_id] = _Request([[] for _ in self.groups], [0] * len(self.groups), None)
+        for g, pages in enumerate(hits):
+            for page in pages:
+                self.pools[g].share(page)
+            req.tables[g].extend(pages)
+        self.prefix_hits += len(hits[0]) if hits else 0
+        self.allocate(req_id, len(token_ids))
+        return (len(hits[0]) if hits else 0) * self.page_size
+
+    def commit(self, req_id, token_ids, num_computed: int) -> None:
+        """After a step: the request's pages that are now full and computed get their hashes, so that later
+        requests can find them."""
+        if not self.prefix_cache:
+            return
+        req = self._requests.get(req_id)
+        if req is None:
+            return
+        ps = self.page_size
+        full = min(num_computed, len(token_ids)) // ps
+        for g in range(len(self.groups)):
+            table = req.tables[g]
+            # the chain continues from the last page of this request that already has a hash
+            i = 0
+            prev = 0
+            while i < full and table[i] in self._page_info[g]:
+                prev = self._page_info[g][table[i]][0]
+                i += 1
+            for j in range(i, full):
+                chunk = tuple(token_ids[j * ps:(j + 1) * ps])
+                prev = self._page_hash(prev, chunk)
+                page = table[j]
+                if prev not in self._by_hash[g]:
+                    self._by_hash[g][prev] = page
+                    self._page_info[g][page] = (prev, chunk)
+                # else the same contents already sit on another page: this one stays anonymous
+
+    def _forget(self, g: int, pages) -> None:
+        """Pages that are handed out for new contents lose their hashes."""
+        for p in pages:
+            info = self._page_info[g].pop(p, None)
+            if info is not None and self._by_hash[g].get(info[0]) == p:
+                del self._by_hash[g][info[0]]
 
     # ------------------------------------------------------------------ queries
     def __contains__(self, req_id) -> bool:
@@ -94,7 +210,10 @@ class CacheManager:
             slot = self.slots.allocate() if self.slots is not None else None
             req = self._requests[req_id] = _Request([[] for _ in self.groups], [0] * len(self.groups), slot)
         for g, n in enumerate(self.pages_needed(req_id, num_tokens)):
-            req.tables[g].extend(self.pools[g].allocate(n))
+            fresh = self.pools[g].allocate(n)
+            if self.prefix_cache:
+                self._forget(g, fresh)
+            req.tables[g].extend(fresh)
         req.num_tokens = max(req.num_tokens, num_tokens)
 
     def release_behind_window(self, req_id, num_computed: int) -> int:
@@ -126,8 +245,13 @@ class CacheManager:
         for g, pool in enumerate(self.pools):
             pool.check()
             held = [p for r in self._requests.values() for p in r.tables[g] if p >= 0]
-            assert len(held) == len(set(held)), f"group {g}: a page is held twice"
+            if not self.prefix_cache:
+                assert len(held) == len(set(held)), f"group {g}: a page is held twice"
             assert set(held) == pool._used, f"group {g}: held pages and the pool's used set differ"
+            for p in set(held):
+                assert pool.ref_count(p) == held.count(p), f"group {g}: page {p} has the wrong number of holders"
+            for h, p in self._by_hash[g].items():
+                assert self._page_info[g][p][0] == h, f"group {g}: the hash tables disagree about page {p}"
         if self.slots is not None:
             self.slots.check()
             held = [r.state_slot for r in self._requests.values()]

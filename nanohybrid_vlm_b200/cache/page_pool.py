@@ -23,6 +23,7 @@ class PagePool:
         self.num_pages = num_pages
         self._free: deque[int] = deque(range(num_pages))
         self._used: set[int] = set()
+        self._refs: dict[int, int] = {}         # holders of each used page (more than one only with prefix reuse)
 
     @property
     def num_free(self) -> int:
@@ -39,7 +40,25 @@ class PagePool:
             raise OutOfPages(f"{n} pages wanted, {len(self._free)} free of {self.num_pages}")
         pages = [self._free.popleft() for _ in range(n)]
         self._used.update(pages)
+        for p in pages:
+            self._refs[p] = 1
         return pages
+
+    def share(self, page: int) -> None:
+        """One more holder for `page`: a used page gets another reference; a free page (whose contents a
+        prefix lookup found still intact) leaves the free queue and is used again."""
+        if page in self._used:
+            self._refs[page] += 1
+        else:
+            self._free.remove(page)
+            self._used.add(page)
+            self._refs[page] = 1
+
+    def is_free(self, page: int) -> bool:
+        return page not in self._used
+
+    def ref_count(self, page: int) -> int:
+        return self._refs.get(page, 0)
 
     def free(self, pages) -> None:
         pages = list(pages)
@@ -47,8 +66,11 @@ class PagePool:
         if bad or len(set(pages)) != len(pages):
             raise RuntimeError(f"pages freed twice or never allocated: {bad or pages}")
         for p in pages:
-            self._used.remove(p)
-            self._free.append(p)
+            self._refs[p] -= 1
+            if self._refs[p] == 0:
+                del self._refs[p]
+                self._used.remove(p)
+                self._free.append(p)
 
     def check(self) -> None:
         """Every page is either free or used, exactly once."""
@@ -56,6 +78,7 @@ class PagePool:
         assert len(set(free)) == len(free), "a page is in the free queue twice"
         assert not (set(free) & self._used), "a page is both free and used"
         assert len(free) + len(self._used) == self.num_pages, "a page was lost"
+        assert set(self._refs) == self._used and all(r > 0 for r in self._refs.values()), "reference counts are off"
 
 
 class StateSlotAllocator:

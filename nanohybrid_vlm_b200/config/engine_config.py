@@ -31,7 +31,7 @@ class Config:
     kvcache_block_size: int = 256            # tokens per cache page (any positive number here)
     num_kvcache_blocks: int = -1             # pages per cache group; -1: sized from free memory
     num_state_slots: int = -1                # slots of fixed-size per-request state; -1: max_num_seqs if a layer needs them, else 0
-    enable_prefix_cache: bool | None = None  # the reference's page reuse by content hash is not built
+    enable_prefix_cache: bool | None = None  # page reuse by content hash; None: on where the model allows it (nanovllm/config.py:393-399)
     dtype: str | torch.dtype | None = None   # None: the checkpoint's own
     seed: int = 0
     # filled by __post_init__
@@ -51,9 +51,6 @@ class Config:
             raise ConfigError("max_num_batched_tokens, max_num_seqs and max_model_len must be positive")
         if not 0.0 < self.gpu_memory_utilization <= 1.0:
             raise ConfigError("gpu_memory_utilization must be in (0, 1]")
-        if self.enable_prefix_cache:
-            raise ConfigError("enable_prefix_cache=True: page reuse by content hash is not built in this engine")
-        self.enable_prefix_cache = False
         self.architecture, self.model_config = load_model_config(self.model)
         self.dtype = parse_dtype(self.dtype) if self.dtype is not None else self.model_config.dtype
         if self.dtype not in (torch.bfloat16, torch.float32):

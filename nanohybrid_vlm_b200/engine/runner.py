@@ -44,7 +44,13 @@ class ModelRunner:
         num_pages = self._size_pools(num_slots)
         config.num_kvcache_blocks, config.num_state_slots = num_pages, num_slots
         counts = [num_pages] * len(self.layout.groups)
-        self.cache = CacheManager(self.layout.groups, self.page_size, counts, num_slots)
+        possible = CacheManager.prefix_cache_possible(self.layout.groups, num_slots)
+        if config.enable_prefix_cache and not possible:
+            raise ValueError("enable_prefix_cache=True, but this model has layers with a window or with per-request "
+                             "state, which shared pages cannot rebuild")
+        config.enable_prefix_cache = possible if config.enable_prefix_cache is None else bool(config.enable_prefix_cache)
+        self.cache = CacheManager(self.layout.groups, self.page_size, counts, num_slots,
+                                  enable_prefix_cache=config.enable_prefix_cache)
         self.storage = CacheStorage(self.layout, spec.order, self.page_size, counts, num_slots, self.dtype, self.device)
         self.builder = BatchBuilder(self.cache, self.vocab_size, self.device,
                                     max_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,

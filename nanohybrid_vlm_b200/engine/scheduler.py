@@ -96,9 +96,10 @@ class Scheduler:
             seq = self.waiting[0]
             if seq.seq_id not in self.cache:
                 live = self.cache.num_live()
-                if live >= self.max_num_seqs or not self.cache.can_allocate(seq.seq_id, len(seq)):
+                if live >= self.max_num_seqs or not self.cache.can_admit(seq.seq_id, seq.token_ids):
                     break
-                self.cache.allocate(seq.seq_id, len(seq))
+                # leading pages that an earlier request left in the cache are shared, not computed again
+                seq.num_cached_tokens = self.cache.admit(seq.seq_id, seq.token_ids)
             remaining = len(seq) - seq.num_cached_tokens
             n = min(remaining, budget, self.max_portion or remaining)
             seq.num_scheduled_tokens = n
@@ -145,6 +146,7 @@ class Scheduler:
         for seq, token in zip(seqs, token_ids):
             seq.num_cached_tokens += seq.num_scheduled_tokens
             seq.num_scheduled_tokens = 0
+            self.cache.commit(seq.seq_id, seq.token_ids, seq.num_cached_tokens)
             if seq.num_cached_tokens < len(seq):
                 self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
                 continue

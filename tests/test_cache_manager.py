@@ -123,3 +123,86 @@ def test_random_orders_keep_the_books_straight(seed):
         cm.free(rid)
     cm.check()
     assert all(pool.num_free == pool.num_pages for pool in cm.pools) and cm.slots.num_free == 5
+
+
+def test_prefix_reuse_shares_full_pages_but_never_the_last():
+    cm = CacheManager([GroupSpec(None)], page_size=4, num_pages=12, enable_prefix_cache=True)
+    a = list(range(100, 114))                                  # 14 tokens: pages 0,1,2 full, page 3 partial
+    assert cm.admit("a", a) == 0 and cm.block_table("a") == [0, 1, 2, 3]
+    cm.commit("a", a, 14)
+    b = a[:10] + [7, 7, 7]                                     # shares two full pages, differs in the third
+    assert cm.can_admit("b", b)
+    assert cm.admit("b", b) == 8 and cm.block_table("b")[:2] == [0, 1] and cm.prefix_hits == 2
+    assert cm.pools[0].ref_count(0) == 2 and cm.pools[0].ref_count(2) == 1
+    cm.check()
+    c = a[:8]                                                  # exactly two pages: the last is never shared
+    assert cm.admit("c", c) == 4 and cm.block_table("c")[0] == 0 and cm.block_table("c")[1] not in (1,)
+    cm.check()
+    cm.free("a")
+    assert cm.pools[0].ref_count(0) == 2 and cm.pools[0].ref_count(1) == 1    # still held by b (and c)
+    cm.free("b"); cm.free("c")
+    assert cm.pools[0].num_free == 12
+    # freed pages keep their contents until they are handed out again: the same prompt finds them
+    assert cm.admit("d", a) == 12 and cm.block_table("d")[:3] == [0, 1, 2]
+    cm.check()
+    cm.free("d")
+    # a page that is handed out for other contents forgets its hash
+    filler = list(range(500, 548))
+    cm.admit("e", filler)                                       # takes all 12 pages
+    cm.free("e")
+    assert cm.admit("f", a) == 0
+    cm.check()
+
+
+def test_prefix_reuse_counts_shared_free_pages_against_the_free_pool():
+    cm = CacheManager([GroupSpec(None)], page_size=4, num_pages=4, enable_prefix_cache=True)
+    a = list(range(16))
+    cm.admit("a", a); cm.commit("a", a, 16); cm.free("a")       # all four pages free, three of them findable
+    b = a[:12] + [99] * 8                                       # needs 5 pages, shares 3: 2 fresh + 3 taken from the free queue
+    assert not cm.can_admit("b", b)
+    with pytest.raises(OutOfPages):
+        cm.admit("b", b)
+    assert "b" not in cm and cm.pools[0].num_free == 4
+    c = a[:12] + [99]                                           # 4 pages, shares 3
+    assert cm.can_admit("c", c) and cm.admit("c", c) == 12
+    cm.check()
+
+
+def test_prefix_reuse_is_refused_for_windows_and_state():
+    with pytest.raises(ValueError):
+        CacheManager([GroupSpec(None), GroupSpec(8)], page_size=4, num_pages=8, enable_prefix_cache=True)
+    with pytest.raises(ValueError):
+        CacheManager([GroupSpec(None)], page_size=4, num_pages=8, num_state_slots=2, enable_prefix_cache=True)
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_prefix_reuse_random_orders(seed):
+    rng = np.random.default_rng(seed)
+    cm = CacheManager([GroupSpec(None)], page_size=4, num_pages=40, enable_prefix_cache=True)
+    stems = [rng.integers(0, 50, 24).tolist() for _ in range(3)]
+    live = {}
+    for step in range(400):
+        if rng.random() < 0.5 and len(live) < 5:
+            toks = stems[int(rng.integers(3))][:int(rng.integers(1, 25))] + rng.integers(50, 60, int(rng.integers(0, 6))).tolist()
+            if cm.can_admit(step, toks):
+                cached = cm.admit(step, toks)
+                assert cached % 4 == 0 and cached < len(toks)
+                live[step] = toks
+                cm.commit(step, toks, len(toks))
+        elif live:
+            rid = int(rng.choice(list(live)))
+            if rng.random() < 0.5:
+                live[rid] = live[rid] + [int(rng.integers(0, 60))]
+                if cm.can_allocate(rid, len(live[rid])):
+                    cm.allocate(rid, len(live[rid]))
+                    cm.commit(rid, live[rid], len(live[rid]))
+                else:
+                    live[rid].pop()
+            else:
+                cm.free(rid)
+                del live[rid]
+        cm.check()
+    for rid in list(live):
+        cm.free(rid)
+    cm.check()
+    assert cm.pools[0].num_free == 40 and cm.prefix_hits > 0

@@ -102,7 +102,7 @@ def test_engine_options(tmp_path):
     assert Config(d, dtype="bfloat16").dtype == torch.bfloat16
     assert Config(write_config(tmp_path, TINY_B)).eos == 7
     for bad in (dict(tensor_parallel_size=2), dict(kvcache_block_size=0), dict(scheduler_policy="x"),
-                dict(gpu_memory_utilization=1.5), dict(enable_prefix_cache=True), dict(dtype="float16"),
+                dict(gpu_memory_utilization=1.5), dict(dtype="float16"),
                 dict(max_num_seqs=0)):
         with pytest.raises(ConfigError):
             Config(d, **bad)

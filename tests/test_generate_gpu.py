@@ -136,3 +136,25 @@ def test_entry_point_checks_its_input(model_dirs):
         SamplingParams(temperature=-1.0)
     with pytest.raises(ValueError):
         SamplingParams(temperature=float("nan"))
+
+
+def test_prefix_reuse_leaves_tokens_unchanged(model_dirs, plain_models):
+    """Requests that share leading pages with an earlier request compute only what is new, and generate the
+    same tokens as the plain implementation (which knows nothing of pages)."""
+    from nanohybrid_vlm_b200 import SamplingParams
+    stem = prompts_for("B", (50,), seed=9)[0]
+    prompts = [stem, stem[:33] + [5, 6, 7], stem, stem[:8]]
+    want = [plain_models["B"].greedy(p, 6) for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    llm = make_llm(model_dirs["B"], "B")
+    assert llm.config.enable_prefix_cache is True
+    first = llm.generate(prompts[:1], sp, use_tqdm=False)
+    assert llm.model_runner.cache.prefix_hits == 0
+    rest = llm.generate(prompts[1:], sp, use_tqdm=False)
+    assert [o["token_ids"] for o in first + rest] == want
+    # pages of 8 tokens: 33 shared tokens -> 4 pages, the whole 50-token stem -> 6 pages, 8 tokens -> none (its only page is its last)
+    assert llm.model_runner.cache.prefix_hits == 4 + 6 + 0
+    llm.model_runner.cache.check()
+    off = make_llm(model_dirs["B"], "B", enable_prefix_cache=False)
+    assert [o["token_ids"] for o in off.generate(prompts, sp, use_tqdm=False)] == want
+    assert off.model_runner.cache.prefix_hits == 0
