@@ -212,7 +212,8 @@ def linear(out, x, weight) -> None:
         torch.mm(x, weight.t(), out=out)
 
 
-SMALL_M = 16    # up to this many tokens the weight-streaming kernel runs instead of the library product
+SMALL_M = 8     # up to this many tokens the weight-streaming kernel runs instead of the library product
+                # (measured on B200: it is ahead up to 8 tokens, the library from 9 on; the kernel itself takes 16)
 
 
 def small_m_ok(x, weight) -> bool:
@@ -285,6 +286,17 @@ def tcgen05_error() -> int:
     """0 unless a bounded wait inside the tcgen05 product ever ran out (synchronises the device)."""
     from .library import load_library
     return load_library().nhv_gemm_tcgen05_error()
+
+
+def linear_stream_k(out, x, weight, mode: int = 0, up_row_offset: int = 0) -> None:
+    """The weight-streaming product for 1 to 16 tokens, whatever `SMALL_M` says (tests, experiments).
+    mode 0: out bfloat16; out float32 selects mode 1; mode 2: weight = [gate; up], out = silu(gate) * up."""
+    _need_cuda(out, x, weight)
+    _contig("out", out); _contig("weight", weight)
+    M, K = x.shape
+    if mode == 0 and out.dtype == torch.float32:
+        mode = 1
+    _small_m(out, x, weight, M, out.shape[1], K, mode, up_row_offset)
 
 
 def stream_k_error() -> int:

@@ -125,26 +125,25 @@ def test_gemm_small_m(ops, M, N, K):
     g = torch.Generator().manual_seed(30)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
-    assert ops.small_m_ok(dev(x), dev(w))
     ref = (x.double() @ w.double().t()).float()
     t = dict(rtol=2e-2, atol=2e-2 * ref.abs().max().item() / 4)
     out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
-    ops.linear(out, dev(x), dev(w))
+    ops.linear_stream_k(out, dev(x), dev(w))
     torch.testing.assert_close(out.cpu().float(), ref, **t)
     out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
-    ops.linear(out32, dev(x), dev(w))
+    ops.linear_stream_k(out32, dev(x), dev(w))
     assert torch.equal(out32.cpu(), out.cpu().float())           # the float32 form is the bfloat16 one, widened
     if N % 2 == 0:
         inter = N // 2
         act = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
-        assert ops.swiglu_first_half(act, dev(x), dev(w))
+        ops.linear_stream_k(act, dev(x), dev(w), mode=2, up_row_offset=inter)
         gu = out.cpu().float()
         want = (gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]).to(torch.bfloat16)
         torch.testing.assert_close(act.cpu().float(), want.float(), rtol=1e-2, atol=1e-3)
     # a row's result does not depend on the other tokens of the batch
     if M > 1:
         one = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
-        ops.linear(one, dev(x[M - 1:M]), dev(w))
+        ops.linear_stream_k(one, dev(x[M - 1:M]), dev(w))
         assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
 
 
