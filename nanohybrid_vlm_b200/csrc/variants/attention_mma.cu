@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
 // sum, unnormalised output) to scratch, and the block that arrives last at that (request, head block)'s
 // counter merges all pieces in block order and writes the output.  No block waits for another.
 constexpr int MAX_DECODE_SEQS = 512;
-constexpr int MIN_TILES = 4;
+constexpr int MIN_TILES = 2;
 #ifndef NHV_ATTN_DECODE_STAGES
 #define NHV_ATTN_DECODE_STAGES 2
 #endif

@@ -264,8 +264,8 @@ _tcgen05_state: dict = {}
 def linear_tcgen05(out, x, weight, mode: int = 0, up_row_offset: int = 0) -> None:
     """out = x @ weight^T for 1 to 128 tokens with tcgen05.mma and tensor-memory accumulators
     (csrc/gemm_tcgen05.cu).  mode 0: out bfloat16; 1: out float32 through bfloat16; 2: weight = [gate; up] rows,
-    out = silu(gate) * up.  Not on the default path: at these sizes the library product is still faster (see
-    the kernel's entry in the design notes); it is kept tested and callable."""
+    out = silu(gate) * up.  Not on the default path: measured on B200 at the 8B layer sizes the library product is
+    still 1.2 to 5 times faster for 32 to 128 tokens; the kernel is kept tested and callable."""
     _need_cuda(out, x, weight)
     _contig("out", out); _contig("weight", weight)
     assert x.dtype == weight.dtype == torch.bfloat16 and x.stride(1) == 1
