@@ -233,13 +233,15 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
   bf16* vbuf = kbuf + 2 * TILE_ELEMS;                        // [2][tile]
   pdl_prologue();
   const int G = nq / nkv;
-  const int kvh = blockIdx.y;
-  int seq = -1, tile = blockIdx.x;
+  // blocks are numbered KV head fastest, then tile; within a request the last tokens (the longest walks over
+  // the keys) get the lowest numbers, so the heavy blocks start first and the light ones fill the tail
+  const int kvh = blockIdx.x;
+  int seq = -1, tile = blockIdx.y;
   for (int s = 0; s < n_seqs; ++s) {
     const int n = cu_q[s + 1] - cu_q[s];
     if (n == 1) continue;                                    // single tokens belong to the decode kernel
     const int nt = (n + tokens_per_block - 1) / tokens_per_block;
-    if (tile < nt) { seq = s; break; }
+    if (tile < nt) { seq = s; tile = nt - 1 - tile; break; }
     tile -= nt;
   }
   if (seq < 0) return;
@@ -620,7 +622,8 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
     ATT_REQUIRE(G <= BN, "attention: a group of %d query heads is beyond the %d rows of a block", G, BN);
     const int tokens_per_block = BN / G;
     const int max_tiles = n_prefill_tokens / tokens_per_block + n_prefill_seqs;
-    dim3 grid(max_tiles, nkv);
+    ATT_REQUIRE(max_tiles <= 65535, "attention: %d tiles of new tokens are beyond the grid's reach", max_tiles);
+    dim3 grid(nkv, max_tiles);
     nhv_launch(attn_prefill_kernel, grid, THREADS, kSmemBytes, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
         n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block);
