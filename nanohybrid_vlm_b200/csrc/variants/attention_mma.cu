@@ -223,13 +223,118 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[KS][4], const bf16* 
 }
 
 // ------------------------------------------------------------------------------------------------ prefill
-__global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
+// Each warp owns MTW row tiles of 16 rows (two for head sizes up to 128, where the accumulators fit the register
+// file; one beyond), so every key and value fragment read from shared memory serves MTW row tiles.  The
+// block's queries stay in shared memory and their fragments are fetched per K slice.  A 64-key tile is walked in
+// two halves of 32 keys to keep the score registers few.
+constexpr int MAX_MTW = D <= 128 ? 2 : 1;
+
+template <int MTW>
+struct PrefillState {
+  float m[MTW][2], l[MTW][2];
+  float o[MTW][DN][4];
+};
+
+template <int MTW>
+__device__ __forceinline__ void warp_tile_prefill(PrefillState<MTW>& st, const bf16* qs, int qrow0, const bf16* ks, const bf16* vs,
+                                                  int key_base, const int (&row_lo)[MTW][2], const int (&row_hi)[MTW][2],
+                                                  int w_lo, int w_hi, float scale_log2) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int kb = h * 32;
+    if (key_base + kb > w_hi || key_base + kb + 32 <= w_lo) continue;      // no row of this warp sees these keys
+    float s[MTW][4][4];
+#pragma unroll
+    for (int mt = 0; mt < MTW; ++mt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+      uint32_t a[MTW][4];
+#pragma unroll
+      for (int mt = 0; mt < MTW; ++mt)
+        ldmatrix_x4(a[mt], qs + tile_off(qrow0 + mt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), 2 * k + (lane >> 4)));
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, ks + tile_off(kb + 8 * j + (lane & 7) + ((lane >> 4) << 3), 2 * k + ((lane >> 3) & 1)));
+#pragma unroll
+        for (int mt = 0; mt < MTW; ++mt) {
+          mma_bf16(s[mt][j], a[mt], b[0], b[1]);
+          mma_bf16(s[mt][j + 1], a[mt], b[2], b[3]);
+        }
+      }
+    }
+    uint32_t pf[MTW][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MTW; ++mt) {
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key_base + kb + 8 * j + ((lane & 3) << 1) + (e & 1);
+          const int i = e >> 1;
+          const float v = (key >= row_lo[mt][i] && key <= row_hi[mt][i]) ? s[mt][j][e] * scale_log2 : -INFINITY;
+          s[mt][j][e] = v;
+          mx[i] = fmaxf(mx[i], v);
+        }
+      float alpha[2], ref[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        const float m_new = fmaxf(st.m[mt][i], mx[i]);
+        ref[i] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[i] = exp2f(st.m[mt][i] - ref[i]);
+        st.m[mt][i] = m_new;
+        st.l[mt][i] *= alpha[i];
+      }
+#pragma unroll
+      for (int n = 0; n < DN; ++n) {
+        st.o[mt][n][0] *= alpha[0]; st.o[mt][n][1] *= alpha[0];
+        st.o[mt][n][2] *= alpha[1]; st.o[mt][n][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float p0 = exp2f(s[mt][j][0] - ref[0]), p1 = exp2f(s[mt][j][1] - ref[0]);
+        const float p2 = exp2f(s[mt][j][2] - ref[1]), p3 = exp2f(s[mt][j][3] - ref[1]);
+        const uint32_t lo = pack_bf16(p0, p1), hi = pack_bf16(p2, p3);
+        const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&lo);
+        const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&hi);
+        st.l[mt][0] += __low2float(lo2) + __high2float(lo2);
+        st.l[mt][1] += __low2float(hi2) + __high2float(hi2);
+        pf[mt][j >> 1][(j & 1) * 2 + 0] = lo;
+        pf[mt][j >> 1][(j & 1) * 2 + 1] = hi;
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int n = 0; n < DN; n += 2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vs + tile_off(kb + 16 * kk + (lane & 7) + (((lane >> 3) & 1) << 3), n + (lane >> 4)));
+#pragma unroll
+        for (int mt = 0; mt < MTW; ++mt) {
+          mma_bf16(st.o[mt][n], pf[mt][kk], b[0], b[1]);
+          mma_bf16(st.o[mt][n + 1], pf[mt][kk], b[2], b[3]);
+        }
+      }
+    }
+  }
+}
+
+template <int MTW>
+__global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) attn_prefill_kernel(
     const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
     const bf16* __restrict__ kv_pages, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_len, int n_seqs, int nq, int nkv, int page_size,
     int n_pages, int window, float scale_log2, int tokens_per_block) {
+  constexpr int PF_ROWS = 64 * MTW;                          // rows (token x head of the group) per block
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);            // [2][tile]
+  bf16* qbuf = reinterpret_cast<bf16*>(smem_raw);            // [PF_ROWS rows]
+  bf16* kbuf = qbuf + MTW * TILE_ELEMS;                      // [2][tile]
   bf16* vbuf = kbuf + 2 * TILE_ELEMS;                        // [2][tile]
   pdl_prologue();
   const int G = nq / nkv;
@@ -251,46 +356,51 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
   const int tq_n = min(tokens_per_block, n_new - t0);
   const int pos0 = total - n_new + t0;                       // position of the block's first token
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int WROWS = 16 * MTW;                            // rows per warp
 
   // stage Q: row R = token * G + head
-  for (int id = threadIdx.x; id < BN * CH; id += THREADS) {
+  for (int id = threadIdx.x; id < PF_ROWS * CH; id += THREADS) {
     const int R = id / CH, c = id - R * CH;
     const int tq = R / G, g = R - tq * G;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (tq < tq_n)
       v = *reinterpret_cast<const uint4*>(q + (size_t)(cu_q[seq] + t0 + tq) * q_stride + (size_t)(kvh * G + g) * D + c * 8);
-    *reinterpret_cast<uint4*>(kbuf + tile_off(R, c)) = v;
+    *reinterpret_cast<uint4*>(qbuf + tile_off(R, c)) = v;
   }
-  __syncthreads();
-  uint32_t qf[KS][4];
-  load_q_frags(qf, kbuf, warp * 16);
-  __syncthreads();
 
-  int row_lo[2], row_hi[2];
+  int row_lo[MTW][2], row_hi[MTW][2];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int R = warp * 16 + (lane >> 2) + 8 * i;
-    const int tq = R / G;
-    if (tq < tq_n) {
-      row_hi[i] = pos0 + tq;
-      row_lo[i] = window > 0 ? max(0, row_hi[i] - window + 1) : 0;
-    } else {
-      row_hi[i] = -1;
-      row_lo[i] = 0;
+  for (int mt = 0; mt < MTW; ++mt)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int R = warp * WROWS + mt * 16 + (lane >> 2) + 8 * i;
+      const int tq = R / G;
+      if (tq < tq_n) {
+        row_hi[mt][i] = pos0 + tq;
+        row_lo[mt][i] = window > 0 ? max(0, row_hi[mt][i] - window + 1) : 0;
+      } else {
+        row_hi[mt][i] = -1;
+        row_lo[mt][i] = 0;
+      }
     }
-  }
   const int pos_hi = pos0 + tq_n - 1;
   const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int key_begin = (first_key / BN) * BN;
   const int n_tiles = (pos_hi - key_begin) / BN + 1;
   // this warp's rows: the span of keys any of them sees (warp-uniform, so whole tiles can be skipped)
-  const int w_tq_lo = (warp * 16) / G, w_tq_hi = min((warp * 16 + 15) / G, tq_n - 1);
+  const int w_tq_lo = (warp * WROWS) / G, w_tq_hi = min((warp * WROWS + WROWS - 1) / G, tq_n - 1);
   const int w_hi = w_tq_lo < tq_n ? pos0 + w_tq_hi : -1;
   const int w_lo = window > 0 ? max(0, pos0 + w_tq_lo - window + 1) : 0;
 
   PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
-  RowState st;
-  init_state(st);
+  PrefillState<MTW> st;
+#pragma unroll
+  for (int mt = 0; mt < MTW; ++mt) {
+    st.m[mt][0] = st.m[mt][1] = -INFINITY;
+    st.l[mt][0] = st.l[mt][1] = 0.f;
+#pragma unroll
+    for (int n = 0; n < DN; ++n) st.o[mt][n][0] = st.o[mt][n][1] = st.o[mt][n][2] = st.o[mt][n][3] = 0.f;
+  }
   int page_next = tile_page(geom, key_begin + BN, pos_hi + 1);
   load_kv_tile(kbuf, vbuf, geom, key_begin, first_key, pos_hi + 1, tile_page(geom, key_begin, pos_hi + 1));
   cp_async_commit();
@@ -306,26 +416,29 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
     } else {
       cp_async_wait<0>();
     }
-    __syncthreads();
+    __syncthreads();                                          // also makes the staged queries visible (first pass)
     const int key_base = key_begin + it * BN;
     if (key_base <= w_hi && key_base + BN > w_lo)
-      warp_tile<8>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, 0, key_base, row_lo, row_hi, scale_log2);
+      warp_tile_prefill<MTW>(st, qbuf, warp * WROWS, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, key_base, row_lo,
+                        row_hi, w_lo, w_hi, scale_log2);
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    float l = st.l[i];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    const int R = warp * 16 + (lane >> 2) + 8 * i;
-    const int tq = R / G, g = R - tq * G;
-    if (tq >= tq_n) continue;
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    bf16* dst = out + (size_t)(cu_q[seq] + t0 + tq) * out_stride + (size_t)(kvh * G + g) * D + ((lane & 3) << 1);
+  for (int mt = 0; mt < MTW; ++mt)
 #pragma unroll
-    for (int n = 0; n < DN; ++n)
-      *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(st.o[n][2 * i] * inv, st.o[n][2 * i + 1] * inv);
-  }
+    for (int i = 0; i < 2; ++i) {
+      float l = st.l[mt][i];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      const int R = warp * WROWS + mt * 16 + (lane >> 2) + 8 * i;
+      const int tq = R / G, g = R - tq * G;
+      if (tq >= tq_n) continue;
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      bf16* dst = out + (size_t)(cu_q[seq] + t0 + tq) * out_stride + (size_t)(kvh * G + g) * D + ((lane & 3) << 1);
+#pragma unroll
+      for (int n = 0; n < DN; ++n)
+        *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(st.o[mt][n][2 * i] * inv, st.o[mt][n][2 * i + 1] * inv);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ decode
@@ -567,7 +680,8 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
   }
 }
 
-constexpr size_t kSmemBytes = (size_t)4 * TILE_ELEMS * sizeof(bf16);                         // prefill: two K and two V tiles
+template <int MTW>
+constexpr size_t prefill_smem_bytes() { return (size_t)(MTW + 4) * TILE_ELEMS * sizeof(bf16); }   // the queries, two K and two V tiles
 constexpr size_t kDecodeSmemBytes = (size_t)(2 * DSTAGES * TILE_ELEMS + Q_ELEMS) * sizeof(bf16);
 static_assert((size_t)4 * TILE_ELEMS * sizeof(bf16) >= (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float),
               "merge buffer must fit the tile buffers");
@@ -610,23 +724,43 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
   const int G = nq / nkv;
   const float scale_log2 = scale * LOG2E;
   static bool attr_set = false;
+  static int sms = 0;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDecodeSmemBytes) != cudaSuccess) {
-      snprintf(g_err, sizeof(g_err), "attention: cannot reserve %zu bytes of shared memory", kSmemBytes);
+    bool ok = cudaFuncSetAttribute(attn_prefill_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)prefill_smem_bytes<1>()) == cudaSuccess &&
+              cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDecodeSmemBytes) == cudaSuccess;
+    if constexpr (MAX_MTW == 2)
+      ok = ok && cudaFuncSetAttribute(attn_prefill_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)prefill_smem_bytes<2>()) == cudaSuccess;
+    int dev = 0;
+    ok = ok && cudaGetDevice(&dev) == cudaSuccess &&
+         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess;
+    if (!ok) {
+      snprintf(g_err, sizeof(g_err), "attention: cannot reserve %zu bytes of shared memory", prefill_smem_bytes<MAX_MTW>());
       return 2;
     }
     attr_set = true;
   }
   if (n_prefill_tokens > 0) {
-    ATT_REQUIRE(G <= BN, "attention: a group of %d query heads is beyond the %d rows of a block", G, BN);
-    const int tokens_per_block = BN / G;
+    ATT_REQUIRE(G <= 64, "attention: a group of %d query heads is beyond the 64 rows of a block", G);
+    // 128 rows a block (every key fragment serves two row tiles) when that still fills the device well;
+    // a row's result is the same either way: the same keys in the same order
+    bool wide = false;
+    if constexpr (MAX_MTW == 2) wide = (long long)nkv * (n_prefill_tokens / (128 / G)) >= 3LL * sms;
+    const int tokens_per_block = (wide ? 128 : 64) / G;
     const int max_tiles = n_prefill_tokens / tokens_per_block + n_prefill_seqs;
     ATT_REQUIRE(max_tiles <= 65535, "attention: %d tiles of new tokens are beyond the grid's reach", max_tiles);
     dim3 grid(nkv, max_tiles);
-    nhv_launch(attn_prefill_kernel, grid, THREADS, kSmemBytes, stream,
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-        n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block);
+    if constexpr (MAX_MTW == 2) {
+      if (wide)
+        nhv_launch(attn_prefill_kernel<2>, grid, THREADS, prefill_smem_bytes<2>(), stream,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
+            n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block);
+    }
+    if (!wide)
+      nhv_launch(attn_prefill_kernel<1>, grid, THREADS, prefill_smem_bytes<1>(), stream,
+          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
+          n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block);
   }
   if (n_decode_seqs > 0) {
     ATT_REQUIRE(scratch_o && scratch_ml && counters && max_pieces > 0 && decode_blocks > 0,
@@ -635,9 +769,7 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
                 n_seqs, MAX_DECODE_SEQS);
     static int resident = 0;                                   // blocks of the decode kernel that fit the device at once
     if (resident == 0) {
-      int per_sm = 0, dev = 0, sms = 0;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      int per_sm = 0;
       if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel, THREADS, kDecodeSmemBytes) != cudaSuccess || per_sm < 1)
         per_sm = 1;
       resident = per_sm * sms;
