@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from . import attention_mma, library
+from . import attention_mma, attention_tcgen05, library
 from .library import KernelError, call
 
 F32, BF16 = 0, 1
@@ -138,6 +138,14 @@ def attention(out, q, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int,
                        nq, nkv, head_dim, scale, window)
 
 
+USE_TCGEN05_ATTENTION = True      # tests switch it off to reach the mma.sync prompt kernel at the same shapes
+
+
+def attention_tcgen05_error(head_dim: int) -> int:
+    """The error word of the tcgen05 attention kernel's bounded waits (0 = none)."""
+    return attention_tcgen05.get(head_dim)[1]()
+
+
 def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_prefill_tokens: int,
                           n_prefill_seqs: int, n_decode_seqs: int, max_kv_len: int, nq: int, nkv: int, head_dim: int,
                           scale: float, window: int = 0) -> None:
@@ -151,6 +159,16 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     assert two == 2 and h == nkv and d == head_dim
     assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
     launch, tile = attention_mma.get(head_dim)
+    if n_prefill_tokens > 0 and USE_TCGEN05_ATTENTION and attention_tcgen05.supports(head_dim, nq, nkv, page_size):
+        # prompt portions on the 5th-generation tensor cores; single tokens stay with the split kernel below
+        library.LAUNCHES += 1
+        attention_tcgen05.get(head_dim)[0](
+            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
+            block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
+            nq, nkv, page_size, n_pages, int(window), float(scale), stream_ptr())
+        if n_decode_seqs == 0:
+            return
+        n_prefill_tokens = n_prefill_seqs = 0
     scratch_o = scratch_ml = counters = None
     max_pieces = blocks = 0
     if n_decode_seqs > 0:

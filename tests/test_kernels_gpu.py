@@ -251,9 +251,15 @@ ATTENTION_SHAPES = [(4, 2, 16, 16, 0), (6, 2, 32, 8, 0), (3, 3, 48, 1, 0), (14, 
                     (34, 1, 64, 16, 300)]
 
 
-@pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
-                                          ("tensor_core", torch.bfloat16)])
-@pytest.mark.parametrize("nq,nkv,d,page,window", ATTENTION_SHAPES)
+# shapes the tcgen05 prompt kernel takes: head sizes in steps of 64, pages in steps of 64 keys
+TCGEN05_SHAPES = [(8, 1, 128, 64, 0), (32, 8, 128, 256, 0), (4, 2, 64, 64, 0), (6, 2, 64, 128, 37), (2, 1, 256, 64, 40),
+                  (12, 4, 192, 64, 0), (3, 1, 128, 64, 0), (5, 5, 64, 192, 300)]
+
+
+@pytest.mark.parametrize("kernel,dtype,nq,nkv,d,page,window",
+                         [(k, t, *shape) for k, t in [("simt", torch.float32), ("simt", torch.bfloat16),
+                                                      ("tensor_core", torch.bfloat16)] for shape in ATTENTION_SHAPES]
+                         + [("tcgen05", torch.bfloat16, *shape) for shape in TCGEN05_SHAPES])
 def test_attention_mixed_batch(ops, kernel, dtype, nq, nkv, d, page, window):
     """Five requests in one batch: a long prompt portion with earlier context, a single decoded token
     after hundreds of keys, a whole short prompt, a decoded token with few keys and a two-token portion;
@@ -299,9 +305,16 @@ def test_attention_mixed_batch(ops, kernel, dtype, nq, nkv, d, page, window):
     if kernel == "simt":
         ops.attention_simt(out, dev(q_all), dev(pages), dev(bt), dev(cu), kv, S, sum(news), nq, nkv, d, scale, window)
     else:
-        ops.attention_tensor_core(out, dev(q_all), dev(pages), dev(bt), dev(cu), kv, S,
-                                  sum(n for n in news if n > 1), sum(1 for n in news if n > 1),
-                                  sum(1 for n in news if n == 1), max(lens), nq, nkv, d, scale, window)
+        # "tensor_core": the mma.sync kernels alone; "tcgen05": prompt portions through the tcgen05 kernel
+        ops.USE_TCGEN05_ATTENTION = kernel == "tcgen05"
+        try:
+            ops.attention_tensor_core(out, dev(q_all), dev(pages), dev(bt), dev(cu), kv, S,
+                                      sum(n for n in news if n > 1), sum(1 for n in news if n > 1),
+                                      sum(1 for n in news if n == 1), max(lens), nq, nkv, d, scale, window)
+        finally:
+            ops.USE_TCGEN05_ATTENTION = True
+        if kernel == "tcgen05":
+            assert ops.attention_tcgen05_error(d) == 0, "a bounded wait of the tcgen05 kernel ran out"
     ref = torch.cat(refs).reshape(-1, nq * d).float()
     t = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(out.cpu().float(), ref, **t)
