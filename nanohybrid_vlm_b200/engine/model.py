@@ -41,6 +41,8 @@ class CausalLM:
 
         self.embedding = TokenEmbedding(spec.embedding.spec, env)
         self._uses.append((spec.embedding, self.embedding))
+        for use in spec.positions:                 # before the layers, so that mixers naming the same spec share them
+            self._uses.append((use, env.position(use.spec)))
         self.blocks = []
         for layer in spec.layers:
             mixer = build(MIXERS, layer.mixer)

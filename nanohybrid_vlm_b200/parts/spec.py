@@ -106,6 +106,9 @@ class ModelSpec:
     final_norm: PartUse
     head: PartUse
     ignored_checkpoint_tensors: tuple[str, ...] = field(default=())
+    # position encodings that act on the embedded tokens or own tensors (kind registered in POSITIONS), with
+    # the prefix of their tensors; one that a mixer names by an equal spec is the same object
+    positions: tuple[PartUse, ...] = field(default=())
 
     def validate(self) -> None:
         if not self.layers or not self.order:

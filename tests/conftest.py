@@ -19,6 +19,12 @@ TINY_B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_siz
               rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=512,
               torch_dtype="float32", hidden_act="silu", attention_bias=False, eos_token_id=7)
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+# a head size and (with pages of 64) a page size that the tcgen05 prompt-attention kernel takes; three query heads
+# share the one KV head, so a block's 128 rows hold 42 tokens and two rows of padding
+TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=120, num_hidden_layers=2,
+              num_attention_heads=3, num_key_value_heads=1, head_dim=64, intermediate_size=200, vocab_size=300,
+              rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=512,
+              torch_dtype="float32", hidden_act="silu", attention_bias=False)
 
 
 def pytest_configure(config):

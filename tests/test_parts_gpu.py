@@ -1,7 +1,8 @@
 """Each part of a layer alone against the plain implementation's function for it, and a toy
 architecture, defined here, whose layers mix a mixer with fixed-size state of its own with attention,
-run one layer twice and let a run read another run's cache: registered, built from random weights and
-stepped without a change to the framework's files."""
+run one layer twice and let a run read another run's cache; another with a windowed layer; a third with a
+feed-forward that routes tokens to experts and a learnt position table: each registered, built from random
+weights and stepped without a change to the framework's files."""
 import json
 
 import numpy as np
@@ -439,3 +440,155 @@ def test_layers_with_a_window_have_pages_of_their_own_and_give_them_back(tmp_pat
                 assert (g - ref[r]).abs().max() <= 0.06 * ref[r].std()
     finally:
         ARCHITECTURES.unregister("ToyWindowLM")
+
+
+# ------------------------------------------------------------------------------------------------ routing and another position encoding
+
+ROUTED = dict(architectures=["ToyRoutedLM"], model_type="toy_routed", hidden_size=40, vocab_size=83, num_experts=3,
+              expert_size=24, num_attention_heads=2, num_key_value_heads=2, head_dim=16, intermediate_size=56,
+              rms_norm_eps=1e-5, max_position_embeddings=96, torch_dtype="float32")
+
+
+def register_routed_toy():
+    """A feed-forward that routes every token to one of its experts, and a position encoding with a learnt table
+    that is added to the embedded tokens (the attention layers then rotate nothing): both defined here."""
+    from nanohybrid_vlm_b200.config import ModelConfig, register_architecture
+    from nanohybrid_vlm_b200.parts import (FEED_FORWARDS, POSITIONS, FeedForward, LayerRun, LayerSpec, ModelSpec,
+                                           ParamDecl, PartUse, PositionEncoding, part)
+
+    class TopOneExperts(FeedForward):
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.E, self.I = int(spec["num_experts"]), int(spec["expert_size"])
+
+        def params(self):
+            H = self.env.hidden_size
+            return [ParamDecl("router.weight", (self.E, H)), ParamDecl("up.weight", (self.E * self.I, H)),
+                    ParamDecl("down.weight", (self.E * H, self.I))]
+
+        def forward(self, x, batch):
+            H = self.env.hidden_size
+            prob = torch.softmax(x.float() @ self.w_router_weight.float().t(), -1)     # router logits in fp32
+            best = prob.argmax(-1)
+            up = self.w_up_weight.float().view(self.E, self.I, H)
+            down = self.w_down_weight.float().view(self.E, H, self.I)
+            hidden = torch.relu(torch.einsum("tih,th->ti", up[best], x.float()))
+            y = torch.einsum("thi,ti->th", down[best], hidden) * prob.gather(1, best[:, None])
+            return y.to(x.dtype)
+
+    class LearntPositions(PositionEncoding):
+        def params(self):
+            return [ParamDecl("weight", (int(self.spec["max_position"]), self.env.hidden_size))]
+
+        def add_to_embeddings(self, h, batch):
+            return (h.float() + self.w_weight.float()[batch.positions.long()]).to(h.dtype)
+
+    FEED_FORWARDS.register("top_one_experts", TopOneExperts, replace=True)
+    POSITIONS.register("learnt", LearntPositions, replace=True)
+
+    def parse(raw):
+        cfg = ModelConfig(architecture="ToyRoutedLM", model_type=raw["model_type"], vocab_size=raw["vocab_size"],
+                          hidden_size=raw["hidden_size"], max_position_embeddings=raw["max_position_embeddings"],
+                          dtype=torch.float32, eos_token_id=None)
+        object.__setattr__(cfg, "raw", raw)
+        return cfg
+
+    def build(cfg):
+        raw = cfg.raw
+        H = raw["hidden_size"]
+        norm = part("rmsnorm", width=H, eps=raw["rms_norm_eps"])
+        attn = part("gqa_attention", num_heads=raw["num_attention_heads"], num_kv_heads=raw["num_key_value_heads"],
+                    head_dim=raw["head_dim"])                           # no q/k norm, nothing rotated
+        experts = part("top_one_experts", num_experts=raw["num_experts"], expert_size=raw["expert_size"])
+        dense = part("swiglu", intermediate_size=raw["intermediate_size"])
+
+        def layer(i, ffn):
+            return LayerSpec(part("prenorm_residual"), PartUse(attn, f"layers.{i}.attn."), PartUse(norm, f"layers.{i}.norm1."),
+                             PartUse(ffn, f"layers.{i}.ffn."), PartUse(norm, f"layers.{i}.norm2."))
+
+        return ModelSpec(architecture="ToyRoutedLM", hidden_size=H, vocab_size=raw["vocab_size"],
+                         max_position=raw["max_position_embeddings"],
+                         embedding=PartUse(part("token_embedding", vocab_size=raw["vocab_size"]), "embed."),
+                         positions=(PartUse(part("learnt", max_position=raw["max_position_embeddings"]), "positions."),),
+                         layers=(layer(0, experts), layer(1, dense)),   # a routed and a dense feed-forward
+                         order=(LayerRun(0), LayerRun(1)),
+                         final_norm=PartUse(norm, "final_norm."),
+                         head=PartUse(part("lm_head", vocab_size=raw["vocab_size"], tied=False), "head."))
+
+    register_architecture("ToyRoutedLM", model_types=("toy_routed",), parse_config=parse, build_spec=build, replace=True)
+
+
+def routed_plain_logits(w, tokens):
+    raw, T = ROUTED, len(tokens)
+    nq, nkv, d, eps, H = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], raw["rms_norm_eps"], raw["hidden_size"]
+    E, I = raw["num_experts"], raw["expert_size"]
+    h = w["embed.weight"][torch.tensor(tokens)] + w["positions.weight"][:T]
+    residual = None
+    for i in range(2):
+        p = f"layers.{i}."
+        if residual is None:
+            residual, x = h, plain.rms_norm(h, w[p + "norm1.weight"], eps)
+        else:
+            x, residual = plain.add_rms_norm(h, residual, w[p + "norm1.weight"], eps)
+        q = plain.linear(x, w[p + "attn.q_proj.weight"]).view(T, nq, d)
+        k = plain.linear(x, w[p + "attn.k_proj.weight"]).view(T, nkv, d)
+        v = plain.linear(x, w[p + "attn.v_proj.weight"]).view(T, nkv, d)
+        o = plain.causal_attention(q, k, v, d ** -0.5)
+        a = plain.linear(o.reshape(T, nq * d), w[p + "attn.o_proj.weight"])
+        x, residual = plain.add_rms_norm(a, residual, w[p + "norm2.weight"], eps)
+        if i == 0:
+            rows = []
+            for t in range(T):
+                prob = torch.softmax(w[p + "ffn.router.weight"] @ x[t], 0)
+                e = int(prob.argmax())
+                up = w[p + "ffn.up.weight"][e * I:(e + 1) * I]
+                down = w[p + "ffn.down.weight"][e * H:(e + 1) * H]
+                rows.append(prob[e] * (down @ torch.relu(up @ x[t])))
+            h = torch.stack(rows)
+        else:
+            h = plain.swiglu_mlp(x, w, p + "ffn.")
+    x, _ = plain.add_rms_norm(h, residual, w["final_norm.weight"], eps)
+    return plain.linear(x, w["head.weight"])
+
+
+def test_a_routed_feed_forward_and_a_learnt_position_table_register_build_and_step(tmp_path):
+    from safetensors.torch import load_file
+    from nanohybrid_vlm_b200.config import ARCHITECTURES, Config
+    from nanohybrid_vlm_b200.engine import ModelRunner, StepItem
+    from nanohybrid_vlm_b200.parts import FEED_FORWARDS, POSITIONS
+    from nanohybrid_vlm_b200.weights import write_random_model
+    register_routed_toy()
+    try:
+        d = write_random_model(str(tmp_path / "routed"), ROUTED, seed=11)
+        w = load_file(f"{d}/model.safetensors")
+        assert w["positions.weight"].shape == (96, 40) and w["layers.0.ffn.router.weight"].shape == (3, 40)
+        assert "layers.1.ffn.gate_proj.weight" in w and "layers.0.attn.q_norm.weight" not in w
+        runner = ModelRunner(Config(d, kvcache_block_size=8, num_kvcache_blocks=24, max_num_seqs=3,
+                                    max_num_batched_tokens=64, max_model_len=96, enforce_eager=True))
+        rng = np.random.default_rng(3)
+        reqs = {"a": rng.integers(0, 83, 50).tolist(), "b": rng.integers(0, 83, 23).tolist()}
+        ref = {r: routed_plain_logits(w, t) for r, t in reqs.items()}
+        experts_used = {int(torch.softmax(w["layers.0.ffn.router.weight"] @ x, 0).argmax())
+                        for x in torch.randn(64, 40, generator=torch.Generator().manual_seed(0))}
+        assert len(experts_used) > 1, "the router of the random model should not send everything to one expert"
+        cuts = {"a": [31, 1, 18], "b": [2, 20, 1]}
+        at, got = {"a": 0, "b": 0}, {"a": [], "b": []}
+        for step in range(3):
+            items = []
+            for r in reqs:
+                n = cuts[r][step]
+                runner.cache.allocate(r, at[r] + n)
+                items.append(StepItem(r, reqs[r][at[r]:at[r] + n], at[r], list(range(n))))
+                at[r] += n
+            logits = runner.step(items).cpu()
+            k = 0
+            for it in items:
+                got[it.req_id].append(logits[k:k + len(it.tokens)])
+                k += len(it.tokens)
+        for r in reqs:
+            torch.testing.assert_close(torch.cat(got[r]), ref[r], rtol=1e-4, atol=2e-5)
+        runner.cache.check()
+    finally:
+        ARCHITECTURES.unregister("ToyRoutedLM")
+        FEED_FORWARDS.unregister("top_one_experts")
+        POSITIONS.unregister("learnt")

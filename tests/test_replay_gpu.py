@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import trace_tools as tt
-from conftest import TINY
+from conftest import TINY, TINY_C
 
 pytestmark = pytest.mark.gpu
 
@@ -76,3 +76,25 @@ def test_float32_logits_do_not_depend_on_the_cutting(name, model_dirs, tmp_path)
         for p in range(len(toks)):
             assert np.array_equal(outs[0][rid][p], outs[1][rid][p]) and np.array_equal(outs[0][rid][p], outs[2][rid][p]), \
                 f"{rid} position {p} differs between ways of cutting"
+
+
+@pytest.mark.parametrize("mode", ["whole", "portions", "mixed"])
+def test_replay_through_the_tcgen05_prompt_kernel(mode, tmp_path):
+    """bfloat16 with a head size of 64 and pages of 64 keys: prompt portions run through the tcgen05 kernel
+    (first and last tiles partly filled, portions beside decoded tokens, pages used again)."""
+    from plain_qwen3 import PlainQwen3
+    from nanohybrid_vlm_b200.kernels import attention_tcgen05
+    from nanohybrid_vlm_b200.weights import write_random_model
+    cfg = TINY_C
+    assert attention_tcgen05.supports(cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"], 64)
+    model_dir = tmp_path / "model"
+    model_dir.mkdir()
+    write_random_model(str(model_dir), cfg, 5)
+    plain = PlainQwen3(str(model_dir))
+    rng = np.random.default_rng(105)
+    reqs = {f"r{i}": rng.integers(0, cfg["vocab_size"], n).tolist() for i, n in enumerate((140, 71, 200, 33, 65, 64, 2, 129))}
+    ref = {rid: plain.logits(t).numpy() for rid, t in reqs.items()}
+    out = tmp_path / "out"
+    out.mkdir()
+    got = tt.run_trace(str(model_dir), "bfloat16", MODES[mode](reqs), str(out), vocab=cfg["vocab_size"], page_size=64)
+    check(got, ref, reqs, "bfloat16")
