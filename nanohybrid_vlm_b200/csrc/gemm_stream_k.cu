@@ -96,6 +96,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Count this block's arrival at a tile: release (what the block wrote before is visible to whoever sees the
+// count) and acquire (what earlier arrivals wrote is visible to this block).  Returns the count before.
+__device__ __forceinline__ int arrive_acq_rel(int* counter) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n" : "=r"(old) : "l"(counter) : "memory");
+  return old;
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { pdl_wait(); }
 __device__ __forceinline__ void launch_dependents() { pdl_launch_dependents(); }
@@ -228,6 +235,67 @@ __global__ void __launch_bounds__(THREADS, NHV_STREAM_K_BK <= 128 ? 2 : 1) gemm_
     clear();
     constexpr int KSTEPS = BK / 16 / CONSUMER_WARPS;        // k-steps per warp per stage
     static_assert(KSTEPS >= 1 && BOX_COLS % (KSTEPS * 16) == 0, "a warp's columns of a stage lie inside one box");
+    const int tid = threadIdx.x;                              // 0..127
+    int deferred_tile = -1, deferred_arrived = 0;
+    // the tile's result from red: the four warps' sums (a tile this block computed alone) or red[0] (gathered)
+    auto write_tile = [&](int tile, bool whole) {
+      for (int id = tid; id < out_rows * X_ROWS; id += CONSUMER_WARPS * 32) {
+        const int m = id / out_rows, r = id - m * out_rows;
+        const int n = tile * out_rows + r;
+        if (m >= p.M || n >= p.N) continue;
+        auto value = [&](int row) -> float {
+          float v = 0.f;
+          if (whole) {
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * ROWS + row) * X_ROWS + m];
+          } else {
+            v = red[row * X_ROWS + m];
+          }
+          return __bfloat162float(__float2bfloat16_rn(v));
+        };
+        float v = value(r);
+        if (p.mode == 2) {
+          const float up = value(32 + r);
+          v = v / (1.0f + expf(-v)) * up;
+        }
+        if (p.mode == 1)
+          reinterpret_cast<float*>(p.y)[(size_t)m * p.ldc + n] = v;
+        else
+          reinterpret_cast<bf16*>(p.y)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v);
+      }
+    };
+    auto tile_pieces = [&](int tile) -> int {
+      const long long t_first = (long long)tile * kb;
+      return unit_owner(t_first + kb - 1, total, G) - unit_owner(t_first, total, G) + 1;
+    };
+    // the block that arrived last at a shared tile: add all blocks' sums in block order and write the tile
+    auto finish_shared_tile = [&](int tile) {
+      const long long t_first = (long long)tile * kb;
+      const int c_first = unit_owner(t_first, total, G);
+      const int pieces = tile_pieces(tile);
+      // gather the partial sums into red[0] first: 16 bytes per thread and piece, four pieces in flight
+      float4* sum4 = reinterpret_cast<float4*>(red);
+      for (int id = tid; id < ROWS * X_ROWS / 4; id += CONSUMER_WARPS * 32) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q0 = 0; q0 < pieces; q0 += 4) {
+          float4 t[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int cc = c_first + min(q0 + j, pieces - 1);
+            const int slot = (int)(unit_begin(cc, total, G) / kb) == tile ? 0 : 1;
+            t[j] = __ldcg(reinterpret_cast<const float4*>(p.scratch + ((size_t)cc * 2 + slot) * ROWS * X_ROWS) + id);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (q0 + j < pieces) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+        }
+        sum4[id] = v;
+      }
+      consumer_sync();
+      write_tile(tile, false);
+      if (tid == 0) p.counters[tile] = 0;                     // ready for the next launch
+      consumer_sync();
+    };
     bool ok = true;
     for (long long u = u0; u < u1 && ok; ++u) {
       const long long i = u - u0;
@@ -280,76 +348,42 @@ __global__ void __launch_bounds__(THREADS, NHV_STREAM_K_BK <= 128 ? 2 : 1) gemm_
       consumer_sync();
       const long long t_first = (long long)tile * kb, t_last = t_first + kb - 1;
       const bool whole = u0 <= t_first && u1 > t_last;
-      const int tid = threadIdx.x;                            // 0..127
-      float* mine = nullptr;
-      int pieces = 1, c_first = c;
-      if (!whole) {
-        c_first = unit_owner(t_first, total, G);
-        pieces = unit_owner(t_last, total, G) - c_first + 1;
-        // slot 0: the tile this block's range starts in; slot 1: a later tile that it only begins
-        const int slot = (int)(u0 / kb) == tile ? 0 : 1;
-        mine = p.scratch + ((size_t)c * 2 + slot) * ROWS * X_ROWS;
-        for (int id = tid; id < ROWS * X_ROWS; id += CONSUMER_WARPS * 32) {
-          float v = 0.f;
-#pragma unroll
-          for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[w * ROWS * X_ROWS + id];
-          mine[id] = v;
-        }
-        __threadfence();
+      if (whole) {
+        write_tile(tile, true);
         consumer_sync();
-        if (tid == 0) s_flag = atomicAdd(&p.counters[tile], 1);
-        consumer_sync();
-        if (s_flag != pieces - 1) { consumer_sync(); continue; }   // another block will finish this tile
-        __threadfence();
+        continue;
       }
-      // this block writes the tile: sum of the 4 warps (whole tile) or of all blocks' partials in block order
-      if (!whole) {
-        // gather the partial sums into red[0] first: 16 bytes per thread and piece, four pieces in flight
-        float4* sum4 = reinterpret_cast<float4*>(red);
-        for (int id = tid; id < ROWS * X_ROWS / 4; id += CONSUMER_WARPS * 32) {
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int q0 = 0; q0 < pieces; q0 += 4) {
-            float4 t[4];
+      // A tile shared with other blocks: park this block's sums in scratch and count the arrival.  The arrival
+      // is a release (the barrier before it orders the other threads' stores before it) and an acquire (the last
+      // block to arrive may read the others' sums), so no thread stands at a fence.
+      // slot 0: the tile this block's range starts in; slot 1: a later tile that it only begins
+      const int slot = (int)(u0 / kb) == tile ? 0 : 1;
+      float* mine = p.scratch + ((size_t)c * 2 + slot) * ROWS * X_ROWS;
+      for (int id = tid; id < ROWS * X_ROWS; id += CONSUMER_WARPS * 32) {
+        float v = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int cc = c_first + min(q0 + j, pieces - 1);
-              const int slot = (int)(unit_begin(cc, total, G) / kb) == tile ? 0 : 1;
-              t[j] = __ldcg(reinterpret_cast<const float4*>(p.scratch + ((size_t)cc * 2 + slot) * ROWS * X_ROWS) + id);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (q0 + j < pieces) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
-          }
-          sum4[id] = v;
-        }
-        consumer_sync();
+        for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[w * ROWS * X_ROWS + id];
+        mine[id] = v;
       }
-      for (int id = tid; id < out_rows * X_ROWS; id += CONSUMER_WARPS * 32) {
-        const int m = id / out_rows, r = id - m * out_rows;
-        const int n = tile * out_rows + r;
-        if (m >= p.M || n >= p.N) continue;
-        auto value = [&](int row) -> float {
-          float v = 0.f;
-          if (whole) {
-#pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) v += red[(w * ROWS + row) * X_ROWS + m];
-          } else {
-            v = red[row * X_ROWS + m];
-          }
-          return __bfloat162float(__float2bfloat16_rn(v));
-        };
-        float v = value(r);
-        if (p.mode == 2) {
-          const float up = value(32 + r);
-          v = v / (1.0f + expf(-v)) * up;
-        }
-        if (p.mode == 1)
-          reinterpret_cast<float*>(p.y)[(size_t)m * p.ldc + n] = v;
-        else
-          reinterpret_cast<bf16*>(p.y)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v);
-      }
-      if (!whole && tid == 0) p.counters[tile] = 0;           // ready for the next launch
       consumer_sync();
+      int arrived = 0;
+      if (tid == 0) arrived = arrive_acq_rel(&p.counters[tile]);
+      if (u != u1 - 1) {
+        // more units follow: keep the stream going and look at the count when it has ended (only the first tile
+        // of a block's range can end in the middle of it)
+        deferred_tile = tile;
+        deferred_arrived = arrived;
+        continue;
+      }
+      if (tid == 0) s_flag = arrived;
+      consumer_sync();
+      if (s_flag == tile_pieces(tile) - 1) finish_shared_tile(tile);
+      consumer_sync();
+    }
+    if (deferred_tile >= 0) {
+      if (tid == 0) s_flag = deferred_arrived;
+      consumer_sync();
+      if (s_flag == tile_pieces(deferred_tile) - 1) finish_shared_tile(deferred_tile);
     }
     if (warp == 0) STAMP(t_slot, 5);
   }
