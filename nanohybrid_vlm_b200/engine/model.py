@@ -87,6 +87,16 @@ class CausalLM:
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.tensors.values())
 
+    def streamed_weights(self) -> list[tuple[torch.Tensor, int]]:
+        """Every matrix that a decode step streams once (each once, though several parts may share it)."""
+        seen, out = set(), []
+        for _, obj in self._uses:
+            for w, mode in obj.streamed_weights():
+                if w.data_ptr() not in seen:
+                    seen.add(w.data_ptr())
+                    out.append((w, mode))
+        return out
+
     # ------------------------------------------------------------------ cache needs
     def cache_needs(self) -> list[PagedKVNeed | FixedStateNeed | None]:
         """For every run of the order: what its mixer keeps between steps (None: nothing, or it reads

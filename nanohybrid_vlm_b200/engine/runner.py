@@ -34,6 +34,7 @@ class ModelRunner:
         else:
             materialize_random(self.model, random_weights_seed)
         self.vocab_size = spec.vocab_size
+        self.decode_copy_bytes = self._prepare_decode_weights()
 
         self.layout = CacheLayout.from_needs(self.model.cache_needs())
         self.page_size = config.kvcache_block_size
@@ -61,6 +62,22 @@ class ModelRunner:
                                                              if b <= config.max_num_seqs]
         self._graphs: dict[int, tuple] = {}
         self._graph_pool = None
+
+    def _prepare_decode_weights(self) -> int:
+        """Tiled copies of the matrices that a decode step streams, for the weight-streaming kernel (before the
+        cache is sized, so that the pool gets what is left).  Returns the bytes they take."""
+        cfg = self.config
+        if self.dtype != torch.bfloat16 or cfg.decode_weight_copy is False:
+            cfg.decode_weight_copy = False
+            return 0
+        weights = [(w, m) for w, m in self.model.streamed_weights() if ops.can_stream_tiled(w, m)]
+        need = sum(ops.tiled_copy_bytes(w, m) for w, m in weights)
+        if cfg.decode_weight_copy is None:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            cfg.decode_weight_copy = need <= free // 4
+        if not cfg.decode_weight_copy:
+            return 0
+        return sum(ops.prepare_streaming(w, m) for w, m in weights)
 
     # ------------------------------------------------------------------ sizing
     def _activation_allowance(self) -> int:

@@ -51,6 +51,9 @@ class GQAttention(Mixer):
     def cache_need(self):
         return PagedKVNeed(self.nkv, self.d, self.window)
 
+    def streamed_weights(self):
+        return [(self.w_qkv_proj_weight, 0), (self.w_o_proj_weight, 0)]
+
     def forward(self, x, batch, cache):
         T = x.shape[0]
         qkv = self.new(T, self.q_size + 2 * self.kv_size)

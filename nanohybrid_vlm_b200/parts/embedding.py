@@ -38,6 +38,9 @@ class LMHead(Part):
     def tie(self, table: torch.Tensor) -> None:
         self.w_weight = table
 
+    def streamed_weights(self):
+        return [(self.w_weight, 1)]
+
     def forward(self, rows_hidden):
         logits = self.new(rows_hidden.shape[0], self.vocab, dtype=torch.float32)
         ops.linear(logits, rows_hidden, self.w_weight)

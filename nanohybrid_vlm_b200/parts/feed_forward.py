@@ -24,6 +24,9 @@ class SwiGLU(FeedForward):
             ParamDecl("down_proj.weight", (H, I)),
         ]
 
+    def streamed_weights(self):
+        return [(self.w_gate_up_proj_weight, 2), (self.w_down_proj_weight, 0)]
+
     def forward(self, x, batch):
         T = x.shape[0]
         act = self.new(T, self.inter)

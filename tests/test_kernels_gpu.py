@@ -147,6 +147,37 @@ def test_gemm_small_m(ops, M, N, K):
         assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 13])
+@pytest.mark.parametrize("N,K", [(384, 96), (1000, 264), (4096, 4096), (24578, 520), (50, 12288)])
+def test_gemm_small_m_from_tiled_weights(ops, M, N, K):
+    """The same products from the tiled copy of the weights (rows and columns padded to the tile, a tile of the
+    fused mode made of 32 gate rows and 32 up rows): bit for bit what the row-major matrix gives, and what
+    ``ops.linear`` takes by itself once ``prepare_streaming`` has registered the copy."""
+    g = torch.Generator().manual_seed(31)
+    x = dev(torch.randn(M, K, generator=g).to(torch.bfloat16))
+    w = dev((torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16))
+    for mode, n_out, dtype in ((0, N, torch.bfloat16), (1, N, torch.float32), (2, N // 2, torch.bfloat16)):
+        want = torch.full((M, n_out), float("nan"), dtype=dtype, device="cuda")
+        ops.linear_stream_k(want, x, w, mode=mode, up_row_offset=N // 2 if mode == 2 else 0)
+        got = torch.full((M, n_out), float("nan"), dtype=dtype, device="cuda")
+        ops.linear_stream_k_tiled(got, x, ops.tile_weight(w, mode), n_out, mode)
+        assert torch.equal(got.cpu(), want.cpu()), f"mode {mode}"
+    assert ops.stream_k_error() == 0
+    if M <= ops.SMALL_M:
+        plain = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        ops.linear(plain, x, w)
+        assert ops.prepare_streaming(w, 0) == ops.tiled_copy_bytes(w, 0) and ops.prepare_streaming(w, 0) == 0
+        through_copy = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.linear(through_copy, x, w)
+        assert torch.equal(through_copy.cpu(), plain.cpu())
+        key = w.data_ptr()
+        assert key in ops._tiled
+        del w, plain
+        import gc
+        gc.collect()
+        assert key not in ops._tiled, "the tiled copy outlived its matrix"
+
+
 @pytest.mark.parametrize("M", [17, 33, 64, 100, 128])
 @pytest.mark.parametrize("N,K", [(384, 96), (1000, 264), (4096, 4096), (4098, 520)])
 def test_gemm_tcgen05(ops, M, N, K):
