@@ -460,19 +460,78 @@ constexpr int Q_ELEMS = 16 * ROW_CH * 8;
 
 __device__ __forceinline__ int tile_owner(long long u, long long total, int G) { return (int)(((u + 1) * G - 1) / total); }
 
+// Decoding straight from the projection's output: with `qkv` set, the kernel itself norms and rotates the new
+// token's query and key heads (the arithmetic and rounding of qk_norm_rope_store.cu: per-head RMS in fp32, rounded
+// to bfloat16, times the weight, rounded, rotated in fp32, rounded) instead of reading `q` and finding the new
+// key and value in the cache; the block that holds a request's last tile puts the new key and value into its
+// tile, and one block per (request, KV head) also stores them in the cache for the steps to come (store = 0: a
+// layer that reads another layer's cache; its keys and values are in the cache already).  One launch less per layer.  Head sizes that are multiples of 32 with rotary_dim a multiple of D / 16.
+struct FusedQK {
+  const bf16* qkv;          // [tokens, (nq + 2 nkv) * D]; null: the plain form
+  const bf16* q_w;          // [D] or null (no norm)
+  const bf16* k_w;
+  const float* cos_sin;     // [max_position, rotary_dim]: cos then sin halves; null: nothing rotates
+  const int* positions;     // [tokens]
+  const int* slot_mapping;  // [tokens] slot of the new key and value in the pool
+  int qkv_stride, rotary_dim, max_position, store;
+  float eps, weight_offset;
+};
+
+constexpr int FVEC = D % 32 == 0 ? D / 32 : 1;               // elements of a head per lane
+
+// One head of the new token in this warp: lane l gets elements [l * FVEC, (l + 1) * FVEC).
+__device__ __forceinline__ void fused_head(float (&v)[FVEC], const bf16* src, const bf16* w, const float* cs,
+                                           const FusedQK& f, int lane) {
+#pragma unroll
+  for (int k = 0; k < FVEC; ++k) v[k] = __bfloat162float(src[lane * FVEC + k]);
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < FVEC; ++k) ss = fmaf(v[k], v[k], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = 1.0f / sqrtf(ss / (float)D + f.eps);
+#pragma unroll
+    for (int k = 0; k < FVEC; ++k) {
+      const float n = __bfloat162float(__float2bfloat16_rn(v[k] * rstd));
+      v[k] = __bfloat162float(__float2bfloat16_rn(n * (__bfloat162float(w[lane * FVEC + k]) + f.weight_offset)));
+    }
+  }
+  if (cs) {
+    const int half = f.rotary_dim >> 1, half_lanes = half / FVEC;
+    const bool first = lane < half_lanes, in_rot = lane < 2 * half_lanes;
+    const int partner = (first ? lane + half_lanes : lane - half_lanes) & 31;
+    const int i0 = (first ? lane : lane - half_lanes) * FVEC;
+#pragma unroll
+    for (int k = 0; k < FVEC; ++k) {
+      const float other = __shfl_sync(0xffffffffu, v[k], partner);
+      if (in_rot) {
+        const float co = cs[i0 + k], si = cs[half + i0 + k];
+        v[k] = first ? v[k] * co - other * si : v[k] * co + other * si;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1) attn_decode_kernel(
     const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride, const bf16* __restrict__ kv_pages,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int n_seqs, int nq, int nkv,
-    int page_size, int n_pages, int window, float scale_log2, int max_pieces) {
+    int page_size, int n_pages, int window, float scale_log2, int max_pieces, const FusedQK fq) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);
   bf16* vbuf = kbuf + DSTAGES * TILE_ELEMS;
   bf16* qbuf = vbuf + DSTAGES * TILE_ELEMS;                   // [16 rows][padded d]
+  __shared__ __align__(16) bf16 s_new[2][D];                  // the new token's key and value (fused form)
   __shared__ unsigned short s_cnt[MAX_DECODE_SEQS];          // tiles of each request (0: not a single-token request)
   __shared__ int s_prefix[MAX_DECODE_SEQS + 1];
   __shared__ int s_flag;
-  pdl_prologue();
+  // The plain form reads the keys that the kernel before it stored, so it waits for that kernel first.  The form
+  // that works from the projection's output finds its work and starts fetching the first tiles of old keys
+  // (written by earlier steps) while the projection winds down, and waits only before it reads qkv.
+  pdl_launch_dependents();
+  bool waited = fq.qkv == nullptr || !fq.store;    // a layer that reads another layer's cache reads keys of this step
+  if (waited) pdl_wait();
   const int G = nq / nkv;
   const int rows_per = min(G, 16);
   const int chunks = (G + 15) / 16;                          // groups of more than 16 heads: several head blocks
@@ -547,13 +606,60 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
       cp_async_commit();
     }
     int page_next = tile_page(geom, key_begin + (DSTAGES - 1) * BN, total);
-    for (int id = threadIdx.x; id < 16 * CH; id += THREADS) {
-      const int R = id / CH, cc = id - R * CH;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (R < gn) v = *reinterpret_cast<const uint4*>(q + tok * q_stride + (size_t)(kvh * G + g0 + R) * D + cc * 8);
-      *reinterpret_cast<uint4*>(qbuf + tile_off(R, cc)) = v;
+    const bool fused = fq.qkv != nullptr;
+    const bool has_last = t_begin + n_tiles == nt;            // this piece ends with the request's newest key
+    if (!waited) {
+      pdl_wait();
+      waited = true;
+    }
+    if (!fused) {
+      for (int id = threadIdx.x; id < 16 * CH; id += THREADS) {
+        const int R = id / CH, cc = id - R * CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (R < gn) v = *reinterpret_cast<const uint4*>(q + tok * q_stride + (size_t)(kvh * G + g0 + R) * D + cc * 8);
+        *reinterpret_cast<uint4*>(qbuf + tile_off(R, cc)) = v;
+      }
+    } else {
+      const bf16* row = fq.qkv + tok * fq.qkv_stride;
+      const float* cs = nullptr;
+      if (fq.cos_sin) {
+        int pos = fq.positions[tok];
+        pos = pos < 0 ? 0 : (pos >= fq.max_position ? fq.max_position - 1 : pos);
+        cs = fq.cos_sin + (size_t)pos * fq.rotary_dim;
+      }
+      for (int R = warp; R < 16; R += THREADS / 32) {         // a warp per query head of the group
+        float v[FVEC];
+        if (R < gn) {
+          fused_head(v, row + (size_t)(kvh * G + g0 + R) * D, fq.q_w, cs, fq, lane);
+        } else {
+#pragma unroll
+          for (int k = 0; k < FVEC; ++k) v[k] = 0.f;
+        }
+        const int e0 = lane * FVEC;
+#pragma unroll
+        for (int k = 0; k < FVEC; ++k) qbuf[tile_off(R, e0 >> 3) + ((e0 & 7) + k)] = __float2bfloat16_rn(v[k]);
+      }
+      if (has_last && fq.store && warp < 2) {                 // warp 0: the new key; warp 1: the new value
+        float v[FVEC];
+        const bf16* src = row + (size_t)(nq + (warp == 0 ? 0 : nkv) + kvh) * D;
+        fused_head(v, src, warp == 0 ? fq.k_w : nullptr, warp == 0 ? cs : nullptr, fq, lane);
+#pragma unroll
+        for (int k = 0; k < FVEC; ++k) s_new[warp][lane * FVEC + k] = __float2bfloat16_rn(v[k]);
+      }
     }
     __syncthreads();
+    if (fused && has_last && fq.store && g0 == 0) {
+      // one block per (request, KV head) stores the new key and value for the steps to come
+      const int slot = fq.slot_mapping[tok];
+      if (slot >= 0 && slot < n_pages * page_size) {
+        const int pg = slot / page_size, off = slot - pg * page_size;
+        for (int id = threadIdx.x; id < 2 * CH; id += THREADS) {
+          const int kv = id / CH, cc = id - kv * CH;
+          bf16* dst = const_cast<bf16*>(kv_pages) + ((((size_t)pg * 2 + kv) * nkv + kvh) * page_size + off) * D + cc * 8;
+          *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&s_new[kv][cc * 8]);
+        }
+      }
+    }
     uint32_t qf[KS][4];
     load_q_frags(qf, qbuf, 0);
     int row_lo[2], row_hi[2];
@@ -577,6 +683,16 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
       cp_async_wait<DSTAGES - 1>();
       __syncthreads();
       const int key_base = key_begin + it * BN;
+      if (fused && fq.store && has_last && it == n_tiles - 1) {
+        // the cache does not hold the newest key and value yet (or is being written): take them from s_new
+        const int r = total - 1 - key_base;
+        for (int id = threadIdx.x; id < 2 * CH; id += THREADS) {
+          const int kv = id / CH, cc = id - kv * CH;
+          *reinterpret_cast<uint4*>((kv == 0 ? kbuf : vbuf) + stage * TILE_ELEMS + tile_off(r, cc)) =
+              *reinterpret_cast<const uint4*>(&s_new[kv][cc * 8]);
+        }
+        __syncthreads();
+      }
       if (key_base + warp * 16 < total && key_base + warp * 16 + 16 > lo)
         warp_tile<2>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, warp * 16, key_base, row_lo, row_hi, scale_log2);
       __syncthreads();
@@ -710,12 +826,12 @@ NHV_API int NHV_FN(nhv_attn_mma_tile_d)() { return BN; }
 // [... * rows * 2] floats and counters [n_seqs * head_blocks] ints that are zero (the kernel leaves them zero),
 // with head_blocks = nkv * ceil(group / 16), rows = min(group, 16), max_pieces >= ceil(longest context / 64) + 1.
 // decode_blocks: the grid of the decode kernel (a few blocks per SM).
-NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
-                                   const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
-                                   int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
-                                   int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
-                                   float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
-                                   cudaStream_t stream) {
+static int attention_launch(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
+                            const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
+                            int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
+                            int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
+                            float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
+                            const FusedQK& fq, cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   ATT_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
   ATT_REQUIRE(q_stride % 8 == 0 && out_stride % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)kv_pages % 16) == 0 &&
@@ -775,9 +891,10 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
       resident = per_sm * sms;
     }
     decode_blocks = resident;
+    if (const char* env = getenv("NHV_ATTN_DECODE_BLOCKS")) { const int v = atoi(env); if (v > 0 && v < resident) decode_blocks = v; }
     nhv_launch(attn_decode_kernel, dim3(decode_blocks), THREADS, kDecodeSmemBytes, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, max_pieces);
+        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, max_pieces, fq);
   }
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {
@@ -785,4 +902,53 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
     return 2;
   }
   return 0;
+}
+
+NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
+                                   const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
+                                   int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
+                                   int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
+                                   float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
+                                   cudaStream_t stream) {
+  FusedQK none = {};
+  return attention_launch(q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs,
+                          n_prefill_tokens, n_prefill_seqs, n_decode_seqs, nq, nkv, page_size, n_pages, window, scale,
+                          scratch_o, scratch_ml, counters, max_pieces, decode_blocks, none, stream);
+}
+
+// 1 if this head size has the form of the decode kernel that works from the projection's output.
+NHV_API int NHV_FN(nhv_attn_mma_can_fuse_d)() { return D % 32 == 0 ? 1 : 0; }
+
+// A step of single tokens only, straight from the projection's output qkv [tokens, (nq + 2 nkv) * D]: the kernel
+// norms and rotates the query and key heads itself and (store != 0) puts the new keys and values into the cache;
+// what qk_norm_rope_store would have done before it.  q_w / k_w null: no norm; cos_sin null: no rotation.
+NHV_API int NHV_FN(nhv_attn_mma_decode_fused_d)(const void* qkv, int qkv_stride, void* out, int out_stride, void* kv_pages,
+                                                const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
+                                                int n_seqs, int nq, int nkv, int page_size, int n_pages, int window,
+                                                float scale, float* scratch_o, float* scratch_ml, int* counters,
+                                                int max_pieces, const void* q_w, const void* k_w, const float* cos_sin,
+                                                const int* positions, const int* slot_mapping, int rotary_dim,
+                                                int max_position, int store, float eps, float weight_offset,
+                                                cudaStream_t stream) {
+  ATT_REQUIRE(D % 32 == 0, "attention: the fused decode form takes head sizes in steps of 32, not %d", D);
+  ATT_REQUIRE(qkv != nullptr && qkv_stride % 8 == 0 && ((uintptr_t)qkv % 16) == 0, "attention: qkv must be 16-byte aligned");
+  ATT_REQUIRE(!cos_sin || (positions && rotary_dim > 0 && rotary_dim <= D && rotary_dim % (2 * FVEC) == 0),
+              "attention: the fused decode form rotates in steps of %d elements, rotary_dim is %d", 2 * FVEC, rotary_dim);
+  ATT_REQUIRE(!store || slot_mapping, "attention: storing the new keys needs the slot mapping");
+  FusedQK fq;
+  fq.qkv = (const bf16*)qkv;
+  fq.q_w = (const bf16*)q_w;
+  fq.k_w = (const bf16*)k_w;
+  fq.cos_sin = cos_sin;
+  fq.positions = positions;
+  fq.slot_mapping = slot_mapping;
+  fq.qkv_stride = qkv_stride;
+  fq.rotary_dim = rotary_dim;
+  fq.max_position = max_position;
+  fq.store = store;
+  fq.eps = eps;
+  fq.weight_offset = weight_offset;
+  return attention_launch(qkv, qkv_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs, 0, 0,
+                          n_seqs, nq, nkv, page_size, n_pages, window, scale, scratch_o, scratch_ml, counters, max_pieces,
+                          1, fq, stream);
 }

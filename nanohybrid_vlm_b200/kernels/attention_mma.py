@@ -21,7 +21,8 @@ def supports(head_dim: int, nq: int, nkv: int) -> bool:
 
 
 def get(head_dim: int):
-    """(launch function, keys per tile) for this head size."""
+    """(launch function, keys per tile, launch function of the decode form that works from the projection's
+    output, or None) for this head size."""
     if head_dim not in _libs:
         from ..csrc.build import ensure_variant
         lib = ctypes.CDLL(ensure_variant("attention_mma.cu", {"NHV_ATTN_D": head_dim}))
@@ -33,9 +34,19 @@ def get(head_dim: int):
         split = getattr(lib, f"nhv_attn_mma_tile_d{head_dim}")
         split.restype = c_int
 
+        fused = getattr(lib, f"nhv_attn_mma_decode_fused_d{head_dim}")
+        fused.argtypes = [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, F, P, P, P, I, P, P, P, P, P, I, I, I, F, F, P]
+        fused.restype = c_int
+        can_fuse = getattr(lib, f"nhv_attn_mma_can_fuse_d{head_dim}")
+        can_fuse.restype = c_int
+
         def launch(*args, _fn=fn, _err=err):
             if _fn(*args) != 0:
                 raise KernelError(_err().decode(errors="replace"))
 
-        _libs[head_dim] = (launch, split())
+        def launch_fused(*args, _fn=fused, _err=err):
+            if _fn(*args) != 0:
+                raise KernelError(_err().decode(errors="replace"))
+
+        _libs[head_dim] = (launch, split(), launch_fused if can_fuse() else None)
     return _libs[head_dim]

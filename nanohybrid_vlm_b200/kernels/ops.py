@@ -140,6 +140,49 @@ def attention(out, q, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int,
                        nq, nkv, head_dim, scale, window)
 
 
+FUSE_DECODE_QK = True             # tests switch it off to compare with the two-kernel form
+
+
+def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int, scale: float,
+                           window: int, q_weight, k_weight, cos_sin, rotary_dim: int, eps: float,
+                           weight_offset: float, store: bool) -> bool:
+    """A step of single tokens only, in bfloat16: attention straight from the projection's output.  The decode
+    kernel norms and rotates the new query and key heads itself and stores the new keys and values (what
+    ``qk_norm_rope_store`` does otherwise, in a launch of its own).  Returns False, having done nothing, when
+    the step or the shapes do not allow it."""
+    if not (FUSE_DECODE_QK and qkv.dtype == torch.bfloat16 and batch.n_prefill_seqs == 0 and batch.n_decode_seqs > 0
+            and attention_mma.supports(head_dim, nq, nkv)):
+        return False
+    launch_fused = attention_mma.get(head_dim)[2]
+    vec = head_dim // 32
+    if launch_fused is None or (cos_sin is not None and (rotary_dim <= 0 or rotary_dim % (2 * vec))):
+        return False
+    if qkv.stride(0) % 8 or qkv.data_ptr() % 16:
+        return False
+    _need_cuda(out, qkv, kv_pages, q_weight, k_weight, cos_sin)
+    _contig("kv_pages", kv_pages)
+    n_pages, two, h, page_size, d = kv_pages.shape
+    assert two == 2 and h == nkv and d == head_dim and kv_pages.dtype == qkv.dtype and out.stride(-1) == 1
+    block_table = tables.block_tables
+    assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
+    n_seqs = batch.n_seqs
+    tile = attention_mma.get(head_dim)[1]
+    group = nq // nkv
+    rows, head_blocks = min(group, 16), nkv * -(-group // 16)
+    max_pieces = -(-batch.max_kv_len // tile) + 1
+    scratch_o = torch.empty(n_seqs * head_blocks * max_pieces * rows * head_dim, dtype=torch.float32, device=qkv.device)
+    scratch_ml = torch.empty(n_seqs * head_blocks * max_pieces * rows * 2, dtype=torch.float32, device=qkv.device)
+    counters = _decode_counters(qkv.device, n_seqs * head_blocks)
+    library.LAUNCHES += 1
+    launch_fused(qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
+                 block_table.stride(0), batch.cu_q.data_ptr(), batch.kv_len.data_ptr(), n_seqs, nq, nkv, page_size,
+                 n_pages, int(window), float(scale), scratch_o.data_ptr(), scratch_ml.data_ptr(), counters.data_ptr(),
+                 max_pieces, _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin), batch.positions.data_ptr(),
+                 tables.slot_mapping.data_ptr(), int(rotary_dim), 0 if cos_sin is None else cos_sin.shape[0],
+                 1 if store else 0, float(eps), float(weight_offset), stream_ptr())
+    return True
+
+
 USE_TCGEN05_ATTENTION = True      # tests switch it off to reach the mma.sync prompt kernel at the same shapes
 
 
@@ -160,7 +203,7 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     n_pages, two, h, page_size, d = kv_pages.shape
     assert two == 2 and h == nkv and d == head_dim
     assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
-    launch, tile = attention_mma.get(head_dim)
+    launch, tile = attention_mma.get(head_dim)[:2]
     if n_prefill_tokens > 0 and USE_TCGEN05_ATTENTION and attention_tcgen05.supports(head_dim, nq, nkv, page_size):
         # prompt portions on the 5th-generation tensor cores; single tokens stay with the split kernel below
         library.LAUNCHES += 1

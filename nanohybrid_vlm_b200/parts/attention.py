@@ -58,15 +58,20 @@ class GQAttention(Mixer):
         T = x.shape[0]
         qkv = self.new(T, self.q_size + 2 * self.kv_size)
         ops.linear(qkv, x, self.w_qkv_proj_weight)
-        q = self.new(T, self.q_size)
         rot = self.position.rotary() if self.position is not None else None
         table, rotary_dim = rot if rot is not None else (None, 0)
-        ops.qk_norm_rope_store(
-            qkv, q, cache.pages if cache.writes else None, cache.tables.slot_mapping, batch.positions,
-            self.w_q_norm_weight if self.qk_norm else None, self.w_k_norm_weight if self.qk_norm else None,
-            table, rotary_dim, self.nq, self.nkv, self.d, self.eps, self.norm_offset)
+        q_w = self.w_q_norm_weight if self.qk_norm else None
+        k_w = self.w_k_norm_weight if self.qk_norm else None
         o = self.new(T, self.q_size)
-        self.attend(o, q, batch, cache)
+        # a step of single tokens: the decode kernel takes qkv as it is (norm, rotation and store inside it)
+        if not ops.attention_decode_fused(o, qkv, cache.pages, cache.tables, batch, self.nq, self.nkv, self.d,
+                                          self.scale, self.window or 0, q_w, k_w, table, rotary_dim, self.eps,
+                                          self.norm_offset, cache.writes):
+            q = self.new(T, self.q_size)
+            ops.qk_norm_rope_store(
+                qkv, q, cache.pages if cache.writes else None, cache.tables.slot_mapping, batch.positions,
+                q_w, k_w, table, rotary_dim, self.nq, self.nkv, self.d, self.eps, self.norm_offset)
+            self.attend(o, q, batch, cache)
         y = self.new(T, self.env.hidden_size)
         ops.linear(y, o, self.w_o_proj_weight)
         return y

@@ -351,6 +351,68 @@ def test_attention_mixed_batch(ops, kernel, dtype, nq, nkv, d, page, window):
     torch.testing.assert_close(out.cpu().float(), ref, **t)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window,rot,norm", [(32, 8, 128, 256, 0, 128, True), (6, 2, 64, 16, 0, 64, True),
+                                                          (4, 4, 32, 8, 19, 16, True), (9, 3, 96, 5, 0, 96, False),
+                                                          (2, 1, 256, 64, 40, 0, True), (34, 1, 64, 16, 300, 32, True)])
+def test_attention_decode_from_the_projection_output(ops, nq, nkv, d, page, window, rot, norm):
+    """A step of single tokens: the decode kernel given qkv as the projection wrote it (it norms, rotates and
+    stores by itself) against the two-kernel form: the same attention output, and the same keys and values in
+    the cache afterwards; and again without storing, as a layer that reads another layer's cache runs."""
+    from types import SimpleNamespace
+    rng = np.random.default_rng(11)
+    g = torch.Generator().manual_seed(11)
+    lens = [611, 1, 64, 65, 200, 7]                          # keys of each request, the new token included
+    S = len(lens)
+    n_pages = sum(-(-L // page) for L in lens) + 3
+    pages = (torch.randn(n_pages, 2, nkv, page, d, generator=g) * 0.5).to(torch.bfloat16)   # stale contents everywhere
+    free = list(rng.permutation(n_pages))
+    tables = [[int(free.pop()) for _ in range(-(-L // page))] for L in lens]
+    width = max(len(t) for t in tables)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    slots = torch.tensor([t[(L - 1) // page] * page + (L - 1) % page for t, L in zip(tables, lens)], dtype=torch.int32)
+    positions = torch.tensor([L - 1 for L in lens], dtype=torch.int32)
+    qkv = torch.randn(S, (nq + 2 * nkv) * d, generator=g).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16) if norm else None
+    table = None
+    if rot:
+        cos, sin = plain.rope_table(rot, 1024, 10000.0)
+        table = dev(torch.cat((cos, sin), -1).contiguous())
+    batch = SimpleNamespace(n_seqs=S, n_prefill_seqs=0, n_prefill_tokens=0, n_decode_seqs=S, max_kv_len=max(lens),
+                            cu_q=dev(torch.arange(S + 1, dtype=torch.int32)), kv_len=dev(torch.tensor(lens, dtype=torch.int32)),
+                            positions=dev(positions), n_tokens=S)
+    views = SimpleNamespace(block_tables=dev(bt), slot_mapping=dev(slots))
+    scale = d ** -0.5
+
+    # the two-kernel form
+    pages_two = dev(pages.clone())
+    q = torch.empty(S, nq * d, dtype=torch.bfloat16, device="cuda")
+    ops.qk_norm_rope_store(dev(qkv), q, pages_two, views.slot_mapping, batch.positions, dev(qw) if norm else None,
+                           dev(kw) if norm else None, table, rot, nq, nkv, d, 1e-6)
+    want = torch.empty(S, nq * d, dtype=torch.bfloat16, device="cuda")
+    ops.attention(want, q, pages_two, views, batch, nq, nkv, d, scale, window)
+
+    # the fused form, storing
+    pages_one = dev(pages.clone())
+    got = torch.full((S, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.attention_decode_fused(got, dev(qkv), pages_one, views, batch, nq, nkv, d, scale, window,
+                                      dev(qw) if norm else None, dev(kw) if norm else None, table, rot, 1e-6, 0.0, True)
+    torch.testing.assert_close(got.cpu().float(), want.cpu().float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(pages_one.cpu().float(), pages_two.cpu().float(), rtol=1e-2, atol=1e-2)
+    changed = (pages_one.cpu() != pages).flatten(2).any(-1)                  # [page, K|V]: only the new slots' pages
+    assert int(changed.sum()) <= 2 * S
+
+    # without storing: the new keys and values are in the cache already (the other run stored them)
+    again = torch.full((S, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    before = pages_two.clone()
+    assert ops.attention_decode_fused(again, dev(qkv), pages_two, views, batch, nq, nkv, d, scale, window,
+                                      dev(qw) if norm else None, dev(kw) if norm else None, table, rot, 1e-6, 0.0, False)
+    torch.testing.assert_close(again.cpu().float(), want.cpu().float(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(pages_two, before)
+
+
 @pytest.mark.parametrize("vocab,rows", [(384, 5), (1000, 3), (151936, 4)])
 def test_sampler(ops, vocab, rows):
     g = torch.Generator().manual_seed(8)
