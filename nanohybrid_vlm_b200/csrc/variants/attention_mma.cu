@@ -749,12 +749,16 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
       }
     }
     if (!whole) {
-      __threadfence();
+      // the arrival is a release (the barrier before it orders the other threads' stores before it) and an
+      // acquire (the last piece to arrive may read the others), so no thread stands at a fence
       __syncthreads();
-      if (threadIdx.x == 0) s_flag = atomicAdd(&counters[unit], 1);
+      if (threadIdx.x == 0) {
+        int old;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n" : "=r"(old) : "l"(counters + unit) : "memory");
+        s_flag = old;
+      }
       __syncthreads();
       if (s_flag == pieces - 1) {                              // the last piece to arrive: merge all, in piece order
-        __threadfence();
         const float* bo = part_o + unit * max_pieces * rows_per * D;
         const float* bml = part_ml + unit * max_pieces * rows_per * 2;
         // the pieces' (max, sum) first: few numbers, loaded side by side into shared memory
@@ -770,13 +774,13 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
           for (int pc = 0; pc < pieces; ++pc) M = fmaxf(M, sml[(pc * gn + R) * 2]);
           float L = 0.f;
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int p0 = 0; p0 < pieces; p0 += 4) {             // four independent 16-byte loads in flight
-            float4 t[4];
+          for (int p0 = 0; p0 < pieces; p0 += 8) {             // eight independent 16-byte loads in flight
+            float4 t[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 8; ++j)
               t[j] = __ldcg(reinterpret_cast<const float4*>(bo + ((size_t)min(p0 + j, pieces - 1) * rows_per + R) * D) + c4);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 8; ++j) {
               if (p0 + j >= pieces) break;
               const float m = sml[((p0 + j) * gn + R) * 2];
               if (m == -INFINITY) continue;
@@ -891,7 +895,6 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
       resident = per_sm * sms;
     }
     decode_blocks = resident;
-    if (const char* env = getenv("NHV_ATTN_DECODE_BLOCKS")) { const int v = atoi(env); if (v > 0 && v < resident) decode_blocks = v; }
     nhv_launch(attn_decode_kernel, dim3(decode_blocks), THREADS, kDecodeSmemBytes, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
         scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, max_pieces, fq);
