@@ -517,6 +517,10 @@ NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int 
 NHV_API int nhv_gemm_stream_k_tiled(void* y, const void* x, const void* Wt, int M, int N, int K, int lda, int ldc, int mode,
                                     float* scratch, int* counters, int counters_len, int grid, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+#ifdef NHV_STREAM_K_TIMING
+  const int timing_slot = lda >> 20;
+  lda &= (1 << 20) - 1;
+#endif
   NHV_REQUIRE(M > 0 && M <= 16, "gemm_stream_k_tiled: takes 1 to 16 tokens, got %d", M);
   NHV_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && lda >= K && ldc >= N,
               "gemm_stream_k_tiled: K and the row stride of x must be multiples of 8 (N=%d K=%d lda=%d)", N, K, lda);
@@ -543,6 +547,9 @@ NHV_API int nhv_gemm_stream_k_tiled(void* y, const void* x, const void* Wt, int 
     p.w_map = it->second;
   }
   NHV_REQUIRE(make_map(&p.x_map, x, M, K, lda, M <= 8 ? 8 : 16), "gemm_stream_k_tiled: cannot encode the tensor map of x [%d, %d]", M, K);
+#ifdef NHV_STREAM_K_TIMING
+  p.lda = lda | (timing_slot << 20);
+#endif
   const long long total = (long long)tiles * kb;
   if (grid > total) grid = (int)total;
   if (M <= 8) return launch<1, NHV_STREAM_K_STAGES>(p, grid, stream);
@@ -621,3 +628,10 @@ NHV_API int nhv_gemm_stream_k_no_alloc(void* y, const void* x, const void* W, in
   if (M <= 8) return launch<1, NHV_STREAM_K_STAGES>(p, grid, stream);
   return launch<2, NHV_STREAM_K_STAGES>(p, grid, stream);
 }
+
+#ifdef NHV_STREAM_K_TIMING
+// Experiments only: the time stamps [8 launches][256 blocks][6 events] in nanoseconds of the global timer.
+NHV_API int nhv_gemm_stream_k_times(unsigned long long* host) {
+  return cudaMemcpyFromSymbol(host, g_times, sizeof(g_times)) == cudaSuccess ? 0 : 1;
+}
+#endif
