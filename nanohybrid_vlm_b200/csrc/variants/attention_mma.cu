@@ -637,7 +637,8 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
         }
         const int e0 = lane * FVEC;
 #pragma unroll
-        for (int k = 0; k < FVEC; ++k) qbuf[tile_off(R, e0 >> 3) + ((e0 & 7) + k)] = __float2bfloat16_rn(v[k]);
+        for (int k = 0; k < FVEC; ++k)      // a lane's elements may straddle two 16-byte chunks (head sizes 96, 160, 192, 224)
+          qbuf[tile_off(R, (e0 + k) >> 3) + ((e0 + k) & 7)] = __float2bfloat16_rn(v[k]);
       }
       if (has_last && fq.store && warp < 2) {                 // warp 0: the new key; warp 1: the new value
         float v[FVEC];

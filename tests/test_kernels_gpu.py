@@ -277,7 +277,7 @@ def reference_attention(q, k, v, scale, window):
     return out
 
 
-ATTENTION_SHAPES = [(4, 2, 16, 16, 0), (6, 2, 32, 8, 0), (3, 3, 48, 1, 0), (14, 2, 80, 5, 0), (8, 1, 128, 64, 0),
+ATTENTION_SHAPES = [(4, 2, 16, 16, 0), (6, 2, 32, 8, 0), (3, 3, 48, 1, 0), (14, 2, 80, 5, 0), (8, 1, 128, 64, 0), (6, 2, 192, 16, 0),
                     (18, 2, 64, 16, 0), (4, 2, 32, 8, 19), (2, 1, 256, 32, 40), (32, 8, 128, 256, 0),
                     (34, 1, 64, 16, 300)]
 
@@ -353,7 +353,9 @@ def test_attention_mixed_batch(ops, kernel, dtype, nq, nkv, d, page, window):
 
 @pytest.mark.parametrize("nq,nkv,d,page,window,rot,norm", [(32, 8, 128, 256, 0, 128, True), (6, 2, 64, 16, 0, 64, True),
                                                           (4, 4, 32, 8, 19, 16, True), (9, 3, 96, 5, 0, 96, False),
-                                                          (2, 1, 256, 64, 40, 0, True), (34, 1, 64, 16, 300, 32, True)])
+                                                          (2, 1, 256, 64, 40, 0, True), (34, 1, 64, 16, 300, 32, True),
+                                                          (6, 2, 192, 16, 0, 192, True), (5, 1, 160, 8, 0, 80, True),
+                                                          (4, 2, 224, 16, 0, 0, False)])
 def test_attention_decode_from_the_projection_output(ops, nq, nkv, d, page, window, rot, norm):
     """A step of single tokens: the decode kernel given qkv as the projection wrote it (it norms, rotates and
     stores by itself) against the two-kernel form: the same attention output, and the same keys and values in
