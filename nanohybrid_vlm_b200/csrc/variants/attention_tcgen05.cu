@@ -3,8 +3,8 @@
 //
 // softmax(q k^T * scale) v per query head, causal, optionally within a window, q of a portion's tokens against
 // all keys of the request that the cache holds (nanovllm/layers/attention.py:67-70 calls a library for this;
-// nanovllm/models/qwen3.py:39 gives the scale).  Scores, softmax and the output sum are fp32; the probabilities
-// are rounded to bfloat16 for the second product, and the row sum adds the rounded values.
+// nanovllm/models/qwen3.py:39 gives the scale).  Scores, softmax, the row sum and the output sum are fp32; the
+// probabilities are rounded to bfloat16 for the second product only.
 //
 // A block owns 128 rows: the 128 / G tokens x G query heads that share one KV head (row = token * G + head), so
 // a key tile read once serves the whole group.  It walks the keys in tiles of 64, which never straddle a page
@@ -165,6 +165,11 @@ __device__ __forceinline__ float fast_exp2(float x) {     // 2^x; -inf gives 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -364,24 +369,25 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
       tmem_ld32_nowait(sr[0], lane_addr + S_COL + (uint32_t)((j & 1) * BN));
       tmem_ld32_nowait(sr[1], lane_addr + S_COL + (uint32_t)((j & 1) * BN) + 32);
       tmem_ld_wait();
-      float x[BN];
+      // x = score * scale in log2 units; the row maximum is taken over the raw scores (the scale is positive)
+      // and the scaling folded into the exponent's multiply-add.  A tile that some row of the block sees only
+      // in part takes the masked path.
       const bool masked = !(key_base >= all_lo && key_base + BN - 1 <= all_hi);
-      if (!masked) {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) x[i] = __uint_as_float(sr[i >> 5][i & 31]) * p.scale_log2;
-      } else {
+      if (masked) {
 #pragma unroll
         for (int i = 0; i < BN; ++i) {
           const int key = key_base + i;
-          x[i] = (key >= row_lo && key <= row_hi) ? __uint_as_float(sr[i >> 5][i & 31]) * p.scale_log2 : -INFINITY;
+          if (!(key >= row_lo && key <= row_hi)) sr[i >> 5][i & 31] = 0xFF800000u;      // -inf
         }
       }
-      float mx0 = x[0], mx1 = x[1], mx2 = x[2], mx3 = x[3];
+      float mx0 = max3(__uint_as_float(sr[0][0]), __uint_as_float(sr[0][1]), __uint_as_float(sr[0][2]));
+      float mx1 = max3(__uint_as_float(sr[0][3]), __uint_as_float(sr[0][4]), __uint_as_float(sr[0][5]));
 #pragma unroll
-      for (int i = 4; i < BN; i += 4) {
-        mx0 = fmaxf(mx0, x[i]); mx1 = fmaxf(mx1, x[i + 1]); mx2 = fmaxf(mx2, x[i + 2]); mx3 = fmaxf(mx3, x[i + 3]);
+      for (int i = 6; i + 3 < BN; i += 4) {
+        mx0 = max3(mx0, __uint_as_float(sr[i >> 5][i & 31]), __uint_as_float(sr[(i + 1) >> 5][(i + 1) & 31]));
+        mx1 = max3(mx1, __uint_as_float(sr[(i + 2) >> 5][(i + 2) & 31]), __uint_as_float(sr[(i + 3) >> 5][(i + 3) & 31]));
       }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const float mx = max3(mx0, mx1, fmaxf(__uint_as_float(sr[1][30]), __uint_as_float(sr[1][31]))) * p.scale_log2;
       float alpha = 1.0f;
       const bool grow = mx > m_run + RESCALE_STEP;              // also the first keys a row sees (m_run = -inf)
       if (grow) {
@@ -389,17 +395,20 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
         m_run = mx;
         l *= alpha;
       }
-      const float ref = m_run == -INFINITY ? 0.f : m_run;
+      const float neg_ref = m_run == -INFINITY ? 0.f : -m_run;
       uint32_t pk[BN / 2];
-      float l0 = 0.f, l1 = 0.f;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < BN; i += 2) {
-        const uint32_t u = pack_bf16(fast_exp2(x[i] - ref), fast_exp2(x[i + 1] - ref));
-        pk[i >> 1] = u;
-        l0 += __uint_as_float(u << 16);                          // the rounded values, as the product uses them
-        l1 += __uint_as_float(u & 0xFFFF0000u);
+      for (int i = 0; i < BN; i += 4) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[i >> 5][i & 31]), p.scale_log2, neg_ref));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[i >> 5][(i & 31) + 1]), p.scale_log2, neg_ref));
+        const float p2 = fast_exp2(fmaf(__uint_as_float(sr[i >> 5][(i & 31) + 2]), p.scale_log2, neg_ref));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(sr[i >> 5][(i & 31) + 3]), p.scale_log2, neg_ref));
+        pk[i >> 1] = pack_bf16(p0, p1);
+        pk[(i >> 1) + 1] = pack_bf16(p2, p3);
+        l0 += p0; l1 += p1; l2 += p2; l3 += p3;                  // the row sum in fp32, before the rounding to bfloat16
       }
-      l += l0 + l1;
+      l += (l0 + l1) + (l2 + l3);
       if (j > 0) {
         // the product of the tile before must be complete: P's buffer is free, and O may be rescaled
         ok = mbar_wait(o_full, (uint32_t)(j - 1) & 1, 8);
