@@ -13,10 +13,11 @@
 // Warp roles.  Warp 0, one lane: TMA producer; per tile one box of 64 keys x 64 columns per 64 columns of the
 // head, for K and for V, from the pool seen as a matrix [pages * 2 * kv_heads * page_size, D], into two stages
 // each.  Warp 1: allocates tensor memory; one lane issues the MMAs: S = Q K^T (M 128, N 64, K = D; Q and K both
-// K-major in the 128-byte swizzle) into one of two S buffers, and O += P V (M 128, N = D, K = 64; P K-major, V as
-// it lies in the cache: MN-major).  Warps 2-5: one thread per row; it reads its row of S from tensor memory,
-// scales, masks, keeps the running maximum and sum, writes the row of P to shared memory, and at the end reads
-// its row of O, divides and stores it.  S of tile j+1 is computed while the rows of tile j are in the softmax.
+// K-major in the 128-byte swizzle) into one of two S buffers, and O += P V (M 128, N = D, K = 64; P read from
+// tensor memory, V as it lies in the cache: MN-major).  Warps 2-5: one thread per row; it reads its row of S from
+// tensor memory, scales, masks, keeps the running maximum and sum, writes the row of P (bfloat16 pairs) over the
+// first half of the S it has just read, and at the end reads its row of O, divides and stores it.  S of tile j+1
+// is computed while the rows of tile j are in the softmax.
 //
 // O stays in tensor memory across tiles.  It is rescaled only when a row's maximum has grown by more than 2^8
 // since the reference it uses (the probabilities are then at most 2^8, which bfloat16 and the fp32 sum hold as
@@ -51,10 +52,9 @@ constexpr int DB = D / 64;                   // 128-byte column blocks of a head
 constexpr int THREADS = 192;
 constexpr int Q_BYTES = DB * BM * 128;
 constexpr int T_BYTES = DB * BN * 128;       // one K tile or one V tile
-constexpr int P_BYTES = BM * 128;
 constexpr int STAGES = 2;
 constexpr int BAR_BYTES = 128;
-constexpr int SMEM_NEED = 1024 + Q_BYTES + P_BYTES + 2 * STAGES * T_BYTES;    // barriers live in the first 128 bytes
+constexpr int SMEM_NEED = 1024 + Q_BYTES + 2 * STAGES * T_BYTES;    // barriers live in the first 128 bytes
 // at least 80 KB, so that an SM never holds more blocks than its tensor memory serves (two of 256 columns)
 constexpr int SMEM_BYTES = SMEM_NEED < 80 * 1024 ? 80 * 1024 : SMEM_NEED;
 constexpr uint32_t TMEM_COLS = (2 * BN + D) <= 256 ? 256 : 512;
@@ -116,6 +116,14 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same with the A operand in tensor memory (one row per lane, two bfloat16 per 32-bit column).
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 // 32 consecutive columns of this thread's lane (no wait: tmem_ld_wait() before the values are used)
 __device__ __forceinline__ void tmem_ld32_nowait(uint32_t (&r)[32], uint32_t taddr) {
@@ -203,8 +211,7 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* tiles = smem_raw + (((raw + BAR_BYTES + 1023u) & ~1023u) - raw);
   unsigned char* q_s = tiles;
-  unsigned char* p_s = q_s + Q_BYTES;
-  unsigned char* k_s = p_s + P_BYTES;                  // [STAGES][T_BYTES]
+  unsigned char* k_s = q_s + Q_BYTES;                  // [STAGES][T_BYTES]
   unsigned char* v_s = k_s + STAGES * T_BYTES;         // [STAGES][T_BYTES]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -309,20 +316,22 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
     if (lane == 0 && n_tiles > 0) {
       const uint32_t idesc_s = instr_desc(BM, BN, false);
       const uint32_t idesc_o = instr_desc(BM, D, true);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      // descriptors are made once: a later K slice, column block or stage only moves the start address, which
+      // sits in the low bits in units of 16 bytes
+      const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
+      const uint64_t k_desc = smem_desc(smem_u32(k_s), 16, 1024);
+      const uint64_t v_desc = smem_desc(smem_u32(v_s), BN * 128, 1024);
       bool ok = true;
       auto issue_qk = [&](int j) -> bool {
         const int st = j & 1;
         if (!mbar_wait(&k_full[st], (uint32_t)(j >> 1) & 1, 4)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(k_s + st * T_BYTES);
+        const uint64_t kd = k_desc + (uint64_t)(st * (T_BYTES >> 4));
         const uint32_t d_addr = tmem_base + S_COL + (uint32_t)((j & 1) * BN);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (uint32_t)(kk & 3) * 32;
-          tc_mma(d_addr, smem_desc(q_addr + (kk >> 2) * (BM * 128) + off, 16, 1024),
-                 smem_desc(k_addr + (kk >> 2) * (BN * 128) + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc_mma(d_addr, q_desc + (uint64_t)(((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4),
+                 kd + (uint64_t)(((kk >> 2) * (BN * 128) + (kk & 3) * 32) >> 4), idesc_s, kk > 0 ? 1u : 0u);
         tc_commit(&k_empty[st]);
         tc_commit(&s_full[j & 1]);
         return true;
@@ -335,11 +344,12 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
         ok = mbar_wait(p_ready, (uint32_t)j & 1, 5) && mbar_wait(&v_full[st], (uint32_t)(j >> 1) & 1, 6);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_s + st * T_BYTES);
+        const uint64_t vd = v_desc + (uint64_t)(st * (T_BYTES >> 4));
+        const uint32_t p_addr = tmem_base + S_COL + (uint32_t)((j & 1) * BN);    // P lies over the first half of this tile's S
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          tc_mma(tmem_base + O_COL, smem_desc(p_addr + kk * 32, 16, 1024),
-                 smem_desc(v_addr + kk * (16 * 128), BN * 128, 1024), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < BN / 16; ++kk)                                       // 8 columns of P and 16 rows of V per 16 keys
+          tc_mma_a_tmem(tmem_base + O_COL, p_addr + kk * 8, vd + (uint64_t)((kk * 16 * 128) >> 4), idesc_o,
+                        (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&v_empty[st]);
         tc_commit(o_full);
       }
@@ -427,11 +437,10 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
           tmem_st_wait();
         }
       }
-      // this row of P: 64 keys = 8 chunks of 16 bytes, chunk c at (c ^ (R & 7))
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(p_s + R * 128 + ((c ^ (R & 7)) << 4)) =
-            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      // this row of P over the first 32 columns of the tile's S (all of which this thread has read): two
+      // bfloat16 per column, the second product's A operand straight from tensor memory
+      tmem_st32(lane_addr + S_COL + (uint32_t)((j & 1) * BN), pk);
+      tmem_st_wait();
       if (key_base + BN > total) {
         // keys beyond the request's last one: their V rows may hold anything (0 * NaN = NaN), so zero them
         ok = mbar_wait(&v_full[j & 1], (uint32_t)(j >> 1) & 1, 10);
@@ -442,8 +451,8 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
           *reinterpret_cast<uint4*>(v_s + (j & 1) * T_BYTES + (rem >> 3) * (BN * 128) + row * 128 + ((rem & 7) << 4)) =
               make_uint4(0, 0, 0, 0);
         }
+        fence_async_smem();
       }
-      fence_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
     }
