@@ -26,6 +26,12 @@ def _add_engine_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--num-kvcache-blocks", type=int, default=-1)
     ap.add_argument("--scheduler-policy", default="decode_first", choices=["decode_first", "prefill_first"])
     ap.add_argument("--enforce-eager", action="store_true")
+    ap.add_argument("--enable-prefix-cache", dest="enable_prefix_cache", action="store_true", default=None,
+                    help="share pages between requests with a common prefix (default: where the model allows it)")
+    ap.add_argument("--no-prefix-cache", dest="enable_prefix_cache", action="store_false")
+    ap.add_argument("--decode-weight-copy", dest="decode_weight_copy", action="store_true", default=None,
+                    help="keep a second, tiled copy of the matrices a decode step streams (default: when it fits)")
+    ap.add_argument("--no-decode-weight-copy", dest="decode_weight_copy", action="store_false")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--random-weights", action="store_true",
                     help="ignore the folder's safetensors and make weights on the device from --seed")
@@ -42,7 +48,8 @@ def cmd_generate(args) -> int:
               max_num_seqs=args.max_num_seqs, max_model_len=args.max_model_len,
               gpu_memory_utilization=args.gpu_memory_utilization, kvcache_block_size=args.kvcache_block_size,
               num_kvcache_blocks=args.num_kvcache_blocks, scheduler_policy=args.scheduler_policy,
-              enforce_eager=args.enforce_eager, seed=args.seed,
+              enforce_eager=args.enforce_eager, seed=args.seed, enable_prefix_cache=args.enable_prefix_cache,
+              decode_weight_copy=args.decode_weight_copy,
               random_weights_seed=args.seed if args.random_weights else None)
     sp = SamplingParams(temperature=args.temperature, max_tokens=args.max_tokens, ignore_eos=args.ignore_eos,
                         seed=args.sampling_seed)
