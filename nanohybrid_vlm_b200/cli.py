@@ -30,7 +30,7 @@ def _add_engine_options(ap: argparse.ArgumentParser) -> None:
                     help="share pages between requests with a common prefix (default: where the model allows it)")
     ap.add_argument("--no-prefix-cache", dest="enable_prefix_cache", action="store_false")
     ap.add_argument("--decode-weight-copy", dest="decode_weight_copy", action="store_true", default=None,
-                    help="keep a second, tiled copy of the matrices a decode step streams (default: when it fits)")
+                    help="keep a second copy of the matrices a decode step streams, laid out per SM (default: when it fits)")
     ap.add_argument("--no-decode-weight-copy", dest="decode_weight_copy", action="store_false")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--random-weights", action="store_true",

@@ -32,7 +32,7 @@ class Config:
     num_kvcache_blocks: int = -1             # pages per cache group; -1: sized from free memory
     num_state_slots: int = -1                # slots of fixed-size per-request state; -1: max_num_seqs if a layer needs them, else 0
     enable_prefix_cache: bool | None = None  # page reuse by content hash; None: on where the model allows it (nanovllm/config.py:393-399)
-    decode_weight_copy: bool | None = None   # a second, tiled copy of the matrices a decode step streams (faster
+    decode_weight_copy: bool | None = None   # a second copy of the matrices a decode step streams, one share per SM (faster
                                              # small batches, twice the weight memory); None: when it fits in a
                                              # quarter of the free device memory
     dtype: str | torch.dtype | None = None   # None: the checkpoint's own

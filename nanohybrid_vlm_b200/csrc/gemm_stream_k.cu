@@ -131,8 +131,6 @@ struct alignas(64) Params {
   float* scratch;       // [grid][2][ROWS][8 * NT] partial sums
   int* counters;        // [tiles], zero between launches
   int M, N, K, lda, ldc, mode, up_row_offset;
-  int tiled;            // 1: W is the tiled copy (see nhv_gemm_stream_k_tiled): box b of unit (tile, k) is rows
-                        // ((tile * kb + k) * BOXES + b) * 64 .. + 63 of a [boxes * 64, 64] matrix
 };
 
 __device__ __forceinline__ long long unit_begin(int c, long long total, int G) { return (long long)c * total / G; }
@@ -190,9 +188,7 @@ __global__ void __launch_bounds__(THREADS, NHV_STREAM_K_BK <= 128 ? 2 : 1) gemm_
 #pragma unroll
         for (int b = 0; b < BOXES; ++b) {
           const int col = k * BK + b * BOX_COLS;
-          if (p.tiled) {         // the unit's boxes follow one another in memory: one copy of BOXES * 64 rows
-            if (b == 0) tma_load_2d(dst, &p.w_map, 0, (int)(((long long)tile * kb + k) * BOXES * ROWS), &full[s]);
-          } else if (p.mode == 2) {     // 32 gate rows, then the same 32 rows of up
+          if (p.mode == 2) {     // 32 gate rows, then the same 32 rows of up
             tma_load_2d(dst + b * W_BOX_BYTES, &p.w_map, col, tile * (ROWS / 2), &full[s]);
             tma_load_2d(dst + b * W_BOX_BYTES + W_BOX_BYTES / 2, &p.w_map, col, p.up_row_offset + tile * (ROWS / 2), &full[s]);
           } else {
@@ -486,7 +482,7 @@ NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int 
   NHV_REQUIRE(tiles <= counters_len, "gemm_stream_k: %d tiles but room for %d counters", tiles, counters_len);
   Params p;
   p.y = y; p.x = (const bf16*)x; p.W = (const bf16*)W; p.scratch = scratch; p.counters = counters;
-  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset; p.tiled = 0;
+  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset;
 #ifdef NHV_STREAM_K_TIMING
   p.lda = lda | (timing_slot << 20);
 #endif
@@ -504,53 +500,6 @@ NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int 
   }
   NHV_REQUIRE(make_map(&p.x_map, x, M, K, lda, M <= 8 ? 8 : 16), "gemm_stream_k: cannot encode the tensor map of x [%d, %d]", M, K);
   const long long total = (long long)tiles * ((K + BK - 1) / BK);
-  if (grid > total) grid = (int)total;
-  if (M <= 8) return launch<1, NHV_STREAM_K_STAGES>(p, grid, stream);
-  return launch<2, NHV_STREAM_K_STAGES>(p, grid, stream);
-}
-
-// The same product from a tiled copy of W, made once when the weights are loaded: the 64 x 64 boxes of W (rows
-// and columns padded with zeros to multiples of 64 and 256; mode 2: a tile's rows are 32 gate rows then the same
-// 32 rows of up) stored one after another, a tile's boxes in the order of their columns, so that every stage of
-// the ring is one contiguous 32 KB of memory instead of 64 pieces of 512 bytes a row apart.
-// Wt: [tiles * ceil(K / 256) * 4 * 64, 64] with tiles = ceil(N / 64) (mode 2: ceil(N / 32)).
-NHV_API int nhv_gemm_stream_k_tiled(void* y, const void* x, const void* Wt, int M, int N, int K, int lda, int ldc, int mode,
-                                    float* scratch, int* counters, int counters_len, int grid, cudaStream_t stream) {
-  if (M == 0 || N == 0) return 0;
-#ifdef NHV_STREAM_K_TIMING
-  const int timing_slot = lda >> 20;
-  lda &= (1 << 20) - 1;
-#endif
-  NHV_REQUIRE(M > 0 && M <= 16, "gemm_stream_k_tiled: takes 1 to 16 tokens, got %d", M);
-  NHV_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && lda >= K && ldc >= N,
-              "gemm_stream_k_tiled: K and the row stride of x must be multiples of 8 (N=%d K=%d lda=%d)", N, K, lda);
-  NHV_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)Wt % 128) == 0, "gemm_stream_k_tiled: x must be 16-byte, the tiled W 128-byte aligned");
-  NHV_REQUIRE(mode >= 0 && mode <= 2 && grid > 0 && scratch && counters, "gemm_stream_k_tiled: bad arguments");
-  const int out_rows = mode == 2 ? ROWS / 2 : ROWS;
-  const int tiles = (N + out_rows - 1) / out_rows;
-  NHV_REQUIRE(tiles <= counters_len, "gemm_stream_k_tiled: %d tiles but room for %d counters", tiles, counters_len);
-  const int kb = (K + BK - 1) / BK;
-  const long long rows = (long long)tiles * kb * BOXES * ROWS;
-  NHV_REQUIRE(rows < (1LL << 31), "gemm_stream_k_tiled: the tiled matrix has %lld rows, beyond a 32-bit coordinate", rows);
-  Params p;
-  p.y = y; p.x = (const bf16*)x; p.W = (const bf16*)Wt; p.scratch = scratch; p.counters = counters;
-  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = 0; p.tiled = 1;
-  {
-    std::lock_guard<std::mutex> lock(g_maps_mutex);
-    const MapKey key{Wt, (int)rows, BOX_COLS, BOXES * ROWS};
-    auto it = g_weight_maps.find(key);
-    if (it == g_weight_maps.end()) {
-      CUtensorMap m;
-      NHV_REQUIRE(make_map(&m, Wt, (int)rows, BOX_COLS, BOX_COLS, BOXES * ROWS), "gemm_stream_k_tiled: cannot encode the tensor map of the tiled W");
-      it = g_weight_maps.emplace(key, m).first;
-    }
-    p.w_map = it->second;
-  }
-  NHV_REQUIRE(make_map(&p.x_map, x, M, K, lda, M <= 8 ? 8 : 16), "gemm_stream_k_tiled: cannot encode the tensor map of x [%d, %d]", M, K);
-#ifdef NHV_STREAM_K_TIMING
-  p.lda = lda | (timing_slot << 20);
-#endif
-  const long long total = (long long)tiles * kb;
   if (grid > total) grid = (int)total;
   if (M <= 8) return launch<1, NHV_STREAM_K_STAGES>(p, grid, stream);
   return launch<2, NHV_STREAM_K_STAGES>(p, grid, stream);
@@ -618,7 +567,7 @@ NHV_API int nhv_gemm_stream_k_no_alloc(void* y, const void* x, const void* W, in
   p.y = y; p.x = (const bf16*)x; p.W = (const bf16*)W;
   p.scratch = reinterpret_cast<float*>(st->base);
   p.counters = reinterpret_cast<int*>(st->base + STATIC_PARTIAL_BYTES);
-  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset; p.tiled = 0;
+  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset;
   const int w_rows = mode == 2 ? up_row_offset + N : N, w_box = mode == 2 ? ROWS / 2 : ROWS;
   // both tensor maps are encoded on the stack: no cache, nothing allocated on the host either
   NHV_REQUIRE(make_map(&p.w_map, W, w_rows, K, K, w_box), "gemm_stream_k_no_alloc: cannot encode the tensor map of W [%d, %d]", w_rows, K);

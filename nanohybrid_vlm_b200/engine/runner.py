@@ -64,14 +64,14 @@ class ModelRunner:
         self._graph_pool = None
 
     def _prepare_decode_weights(self) -> int:
-        """Tiled copies of the matrices that a decode step streams, for the weight-streaming kernel (before the
-        cache is sized, so that the pool gets what is left).  Returns the bytes they take."""
+        """Second copies of the matrices that a decode step streams, laid out for the weight-streaming kernel
+        (before the cache is sized, so that the pool gets what is left).  Returns the bytes they take."""
         cfg = self.config
         if self.dtype != torch.bfloat16 or cfg.decode_weight_copy is False:
             cfg.decode_weight_copy = False
             return 0
-        weights = [(w, m) for w, m in self.model.streamed_weights() if ops.can_stream_tiled(w, m)]
-        need = sum(ops.tiled_copy_bytes(w, m) for w, m in weights)
+        weights = [(w, m) for w, m in self.model.streamed_weights() if ops.can_stream_slabs(w, m)]
+        need = sum(ops.slab_copy_bytes(w, m) for w, m in weights)
         if cfg.decode_weight_copy is None:
             free, _ = torch.cuda.mem_get_info(self.device)
             cfg.decode_weight_copy = need <= free // 4

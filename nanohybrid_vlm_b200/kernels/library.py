@@ -28,7 +28,8 @@ _SIGNATURES = {
     "nhv_sample": [P, P, I, P, P, P, I, I, P],
     "nhv_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, P],
     "nhv_gemm_stream_k": [P, P, P, I, I, I, I, I, I, I, P, P, I, I, P],
-    "nhv_gemm_stream_k_tiled": [P, P, P, I, I, I, I, I, I, P, P, I, I, P],
+    "nhv_gemm_slab": [P, P, P, I, I, I, I, I, I, I, P],
+    "nhv_gemm_slab_geometry": [I, I, I, I, P, P, P, P, P],
     "nhv_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, I, P],
 }
 

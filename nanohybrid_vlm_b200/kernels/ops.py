@@ -313,10 +313,10 @@ def _small_m(out, x, weight, M: int, N: int, K: int, mode: int, up_row_offset: i
                                      torch.zeros(STREAM_K_COUNTERS, dtype=torch.int32, device=dev))
     sms, scratch, counters = st
     tiles = -(-N // (32 if mode == 2 else 64))
-    tiled = _tiled.get(weight.data_ptr())
-    if tiled is not None and tiled[0]() is weight and tiled[2] == mode:
-        call("nhv_gemm_stream_k_tiled", out.data_ptr(), x.data_ptr(), tiled[1].data_ptr(), M, N, K, x.stride(0), N, mode,
-             scratch.data_ptr(), counters.data_ptr(), STREAM_K_COUNTERS, sms, stream_ptr())
+    slab = _slabs.get(weight.data_ptr())
+    if slab is not None and slab[0]() is weight and slab[2] == mode and M <= SLAB_MAX_M:
+        call("nhv_gemm_slab", out.data_ptr(), x.data_ptr(), slab[1].data_ptr(), M, N, K, x.stride(0), N, mode, sms,
+             stream_ptr())
         return
     if tiles > STREAM_K_COUNTERS:
         call("nhv_gemm_small_m", out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), N, mode,
@@ -326,81 +326,101 @@ def _small_m(out, x, weight, M: int, N: int, K: int, mode: int, up_row_offset: i
          up_row_offset, scratch.data_ptr(), counters.data_ptr(), STREAM_K_COUNTERS, sms, stream_ptr())
 
 
-_tiled: dict = {}       # data pointer of a weight matrix -> (weak reference to it, its tiled copy, mode)
+SLAB_MAX_M = 8          # tokens that csrc/gemm_slab.cu takes
+_slabs: dict = {}       # data pointer of a weight matrix -> (weak reference to it, its copy for gemm_slab.cu, mode)
 
 
-def tiled_copy_bytes(weight: torch.Tensor, mode: int) -> int:
+def slab_copy_bytes(weight: torch.Tensor, mode: int) -> int:
     n, k = weight.shape
-    tiles = -(-(n // 2) // 32) if mode == 2 else -(-n // 64)
-    return tiles * 64 * (-(-k // 256) * 256) * 2
+    geo = slab_geometry(n // 2 if mode == 2 else n, k, mode, _sm_count(weight.device))
+    return geo["blocks"] * geo["slab_bytes"]
 
 
-def can_stream_tiled(weight: torch.Tensor, mode: int) -> bool:
-    n, k = weight.shape
-    tiles = -(-(n // 2) // 32) if mode == 2 else -(-n // 64)
-    return (weight.is_cuda and weight.dtype == torch.bfloat16 and weight.dim() == 2 and k % 8 == 0
-            and tiles <= STREAM_K_COUNTERS and tiles * (-(-k // 256)) * 256 < 2 ** 31)
+def can_stream_slabs(weight: torch.Tensor, mode: int) -> bool:
+    return (weight.is_cuda and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[1] % 8 == 0
+            and weight.shape[0] >= (2 if mode == 2 else 1))
 
 
 def prepare_streaming(weight: torch.Tensor, mode: int) -> int:
-    """Keep a tiled copy of ``weight`` for the weight-streaming kernel (``tile_weight``); products of up to
-    ``SMALL_M`` tokens with this matrix in this mode then read the copy: every stage of the kernel's ring is one
-    contiguous 32 KB of memory, which HBM serves faster than 64 pieces of 512 bytes a row apart (measured on
-    B200: 76 instead of 87 us for the four matrices of an 8B-sized layer).  The copy lives as long as the matrix.
-    Returns the bytes it takes (0 if the matrix cannot be streamed)."""
-    if not can_stream_tiled(weight, mode):
+    """Keep a second copy of ``weight`` laid out for ``csrc/gemm_slab.cu`` (``slab_weight``); products of up to 8
+    tokens with this matrix in this mode then read the copy: one share of rows per SM, every stage of the kernel's
+    ring one contiguous copy of up to 32 KB, no sums across blocks.  Measured on B200 for the four matrices of an
+    8B-sized layer: 73 us, against 87 us for the stream-K kernel on the row-major matrix (64 pieces of 512 bytes a
+    row apart per stage, and a fix-up of shared tiles at the end of every launch).  The copy lives as long as the
+    matrix.  Returns the bytes it takes (0 if the matrix cannot be streamed this way)."""
+    if not can_stream_slabs(weight, mode):
         return 0
     key = weight.data_ptr()
-    old = _tiled.get(key)
+    old = _slabs.get(key)
     if old is not None and old[0]() is weight and old[2] == mode:
         return 0
-    copy = tile_weight(weight, mode)
-    _tiled[key] = (weakref.ref(weight), copy, mode)
-    weakref.finalize(weight, _drop_tiled, key, copy.data_ptr())
+    copy = slab_weight(weight, mode, _sm_count(weight.device))
+    _slabs[key] = (weakref.ref(weight), copy, mode)
+    weakref.finalize(weight, _drop_slab, key, copy.data_ptr())
     return copy.numel() * copy.element_size()
 
 
-def _drop_tiled(key: int, copy_ptr: int) -> None:
-    entry = _tiled.get(key)
+def _drop_slab(key: int, copy_ptr: int) -> None:
+    entry = _slabs.get(key)
     if entry is not None and entry[1].data_ptr() == copy_ptr:
-        del _tiled[key]
+        del _slabs[key]
 
 
-def tile_weight(weight: torch.Tensor, mode: int = 0) -> torch.Tensor:
-    """The tiled copy of a weight matrix [N, K] that ``linear_stream_k_tiled`` reads: 64 x 64 boxes stored one
-    after another, a tile's boxes in column order, rows and columns padded with zeros to multiples of 64 and 256.
-    mode 2: ``weight`` is [gate rows; up rows] and a tile is 32 gate rows followed by the same 32 rows of up."""
+def slab_geometry(N: int, K: int, mode: int, sms: int) -> dict:
+    """How ``csrc/gemm_slab.cu`` cuts a matrix with N result columns and K columns on a device with ``sms`` SMs."""
+    import ctypes
+    blocks, rpb, nb, ks = (ctypes.c_int() for _ in range(4))
+    slab_bytes = ctypes.c_longlong()
+    call("nhv_gemm_slab_geometry", N, K, mode, sms, ctypes.addressof(blocks), ctypes.addressof(rpb), ctypes.addressof(nb),
+         ctypes.addressof(ks), ctypes.addressof(slab_bytes))
+    return dict(blocks=blocks.value, rpb=rpb.value, nb=nb.value, ks=ks.value, slab_bytes=slab_bytes.value)
+
+
+def slab_weight(weight: torch.Tensor, mode: int, sms: int) -> torch.Tensor:
+    """The copy of a weight matrix [N, K] (mode 2: [gate rows; up rows]) that ``linear_slab`` reads: one share of
+    rows per block, walked in sub-tiles of up to 64 rows over stages of nb * 64 columns; the bytes of a stage lie
+    together, box by box (64 columns), row by row (128 bytes; mode 2: a sub-tile's gate rows, then its up rows), the
+    16-byte chunks of row r of a box exchanged by c ^ (r & 7).  Rows and columns beyond the matrix are zeros."""
     assert weight.dtype == torch.bfloat16 and weight.dim() == 2
-    n, k = weight.shape
-    kp = -(-k // 256) * 256
-    if mode == 2:
-        inter = n // 2
-        tiles = -(-inter // 32)
-        w = torch.zeros(2, tiles * 32, kp, dtype=weight.dtype, device=weight.device)
-        w[0, :inter, :k] = weight[:inter]
-        w[1, :inter, :k] = weight[inter:]
-        w = w.view(2, tiles, 32, kp).permute(1, 0, 2, 3).reshape(tiles, 64, kp)
-    else:
-        tiles = -(-n // 64)
-        w = torch.zeros(tiles * 64, kp, dtype=weight.dtype, device=weight.device)
-        w[:n, :k] = weight
-        w = w.view(tiles, 64, kp)
-    return w.view(tiles, 64, kp // 64, 64).permute(0, 2, 1, 3).contiguous().view(-1, 64)
+    rows, K = weight.shape
+    N = rows // 2 if mode == 2 else rows
+    geo = slab_geometry(N, K, mode, sms)
+    G, r, nb, ks = geo["blocks"], geo["rpb"], geo["nb"], geo["ks"]
+    th = 32 if mode == 2 else 64
+    k_pad = ks * nb * 64
+
+    def padded(part):                                    # [N, K] -> [G, r, ks, nb, 8 chunks, 8 elements]
+        w = torch.zeros(G * r, k_pad, dtype=weight.dtype, device=weight.device)
+        w[:N, :K] = part
+        return w.view(G, r, ks, nb, 8, 8)
+
+    kinds = [padded(weight[:N]), padded(weight[N:])] if mode == 2 else [padded(weight)]
+    chunk = torch.arange(8, device=weight.device)
+    pieces = []
+    for t0 in range(0, r, th):
+        h = min(th, r - t0)
+        sub = torch.cat([kind[:, t0:t0 + h] for kind in kinds], 1)                           # [G, rows of the box, ks, nb, 8, 8]
+        rows_t = sub.shape[1]
+        src = chunk[None, :] ^ (torch.arange(rows_t, device=weight.device)[:, None] & 7)     # [rows, 8]: where chunk c' comes from
+        sub = torch.gather(sub, 4, src[None, :, None, None, :, None].expand(G, rows_t, ks, nb, 8, 8))
+        pieces.append(sub.permute(0, 2, 3, 1, 4, 5).reshape(G, -1))                          # [G, ks, nb, rows, 64]
+    out = torch.cat(pieces, 1).contiguous()
+    assert out.shape[1] * 2 == geo["slab_bytes"], (out.shape, geo)
+    return out.view(-1)
 
 
-def linear_stream_k_tiled(out, x, tiled_weight, N: int, mode: int = 0) -> None:
-    """The weight-streaming product from a tiled copy of the weights (``tile_weight``); out [M, N]."""
-    _need_cuda(out, x, tiled_weight)
+def linear_slab(out, x, slabs, N: int, mode: int, sms: int) -> None:
+    """out [M, N] = x [M, K] @ W^T for up to 8 tokens from the copy made by ``slab_weight`` (mode 2: silu(gate) * up)."""
+    _need_cuda(out, x, slabs)
     M, K = x.shape
-    dev = x.device
-    st = _stream_k_state.get(dev)
-    if st is None:
-        sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        st = _stream_k_state[dev] = (sms, torch.zeros(sms * 2 * 64 * 16, dtype=torch.float32, device=dev),
-                                     torch.zeros(STREAM_K_COUNTERS, dtype=torch.int32, device=dev))
-    sms, scratch, counters = st
-    call("nhv_gemm_stream_k_tiled", out.data_ptr(), x.data_ptr(), tiled_weight.data_ptr(), M, N, K, x.stride(0),
-         out.stride(0), mode, scratch.data_ptr(), counters.data_ptr(), STREAM_K_COUNTERS, sms, stream_ptr())
+    call("nhv_gemm_slab", out.data_ptr(), x.data_ptr(), slabs.data_ptr(), M, N, K, x.stride(0), out.stride(0), mode, sms,
+         stream_ptr())
+
+
+def slab_error() -> int:
+    """0 unless a bounded wait inside the slab product ever ran out (synchronises the device)."""
+    from .library import load_library
+    return load_library().nhv_gemm_slab_error()
 
 
 _tcgen05_state: dict = {}

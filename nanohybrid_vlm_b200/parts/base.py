@@ -98,7 +98,7 @@ class Part:
     def streamed_weights(self) -> list[tuple[torch.Tensor, int]]:
         """The matrices that a decode step reads once from end to end, with the mode in which
         ``kernels.ops`` streams them (0: plain product, 1: fp32 logits, 2: [gate; up] rows with SiLU).  The
-        engine may keep a second, tiled copy of each for the weight-streaming kernel.  Default: none."""
+        engine may keep a second copy of each, laid out for the weight-streaming kernel.  Default: none."""
         return []
 
     def new(self, *shape, dtype=None) -> torch.Tensor:

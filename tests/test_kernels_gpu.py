@@ -147,35 +147,49 @@ def test_gemm_small_m(ops, M, N, K):
         assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 13])
-@pytest.mark.parametrize("N,K", [(384, 96), (1000, 264), (4096, 4096), (24578, 520), (50, 12288)])
-def test_gemm_small_m_from_tiled_weights(ops, M, N, K):
-    """The same products from the tiled copy of the weights (rows and columns padded to the tile, a tile of the
-    fused mode made of 32 gate rows and 32 up rows): bit for bit what the row-major matrix gives, and what
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("N,K", [(384, 96), (1000, 264), (4096, 4096), (24578, 520), (50, 12288), (7, 40), (6144, 4096)])
+def test_gemm_from_slabs(ops, M, N, K):
+    """The decode step's products from the copy of the weights that is cut into one share of rows per SM
+    (csrc/gemm_slab.cu): plain, float32 output and the fused SwiGLU half, against fp64; shapes whose shares are 1,
+    3, 7, 28, 42 and 167 rows, whose columns need padding to the stage, and whose last share is short; and what
     ``ops.linear`` takes by itself once ``prepare_streaming`` has registered the copy."""
     g = torch.Generator().manual_seed(31)
-    x = dev(torch.randn(M, K, generator=g).to(torch.bfloat16))
-    w = dev((torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16))
-    for mode, n_out, dtype in ((0, N, torch.bfloat16), (1, N, torch.float32), (2, N // 2, torch.bfloat16)):
-        want = torch.full((M, n_out), float("nan"), dtype=dtype, device="cuda")
-        ops.linear_stream_k(want, x, w, mode=mode, up_row_offset=N // 2 if mode == 2 else 0)
-        got = torch.full((M, n_out), float("nan"), dtype=dtype, device="cuda")
-        ops.linear_stream_k_tiled(got, x, ops.tile_weight(w, mode), n_out, mode)
-        assert torch.equal(got.cpu(), want.cpu()), f"mode {mode}"
-    assert ops.stream_k_error() == 0
-    if M <= ops.SMALL_M:
-        plain = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-        ops.linear(plain, x, w)
-        assert ops.prepare_streaming(w, 0) == ops.tiled_copy_bytes(w, 0) and ops.prepare_streaming(w, 0) == 0
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ref = (x.double() @ w.double().t()).float()
+    t = dict(rtol=2e-2, atol=2e-2 * ref.abs().max().item() / 4)
+    xd, wd = dev(x), dev(w)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear_slab(out, xd, ops.slab_weight(wd, 0, sms), N, 0, sms)
+    torch.testing.assert_close(out.cpu().float(), ref, **t)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    ops.linear_slab(out32, xd, ops.slab_weight(wd, 1, sms), N, 1, sms)
+    assert torch.equal(out32.cpu(), out.cpu().float())           # the float32 form is the bfloat16 one, widened
+    if N % 2 == 0:
+        inter = N // 2
+        act = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.linear_slab(act, xd, ops.slab_weight(wd, 2, sms), inter, 2, sms)
+        gu = out.cpu().float()
+        want = (gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]).to(torch.bfloat16)
+        torch.testing.assert_close(act.cpu().float(), want.float(), rtol=1e-2, atol=1e-3)
+    if M > 1:                                                    # a row's result does not depend on the other tokens
+        one = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+        ops.linear_slab(one, xd[M - 1:M], ops.slab_weight(wd, 0, sms), N, 0, sms)
+        assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
+    assert ops.slab_error() == 0
+    if K % 8 == 0:
+        assert ops.prepare_streaming(wd, 0) == ops.slab_copy_bytes(wd, 0) and ops.prepare_streaming(wd, 0) == 0
         through_copy = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
-        ops.linear(through_copy, x, w)
-        assert torch.equal(through_copy.cpu(), plain.cpu())
-        key = w.data_ptr()
-        assert key in ops._tiled
-        del w, plain
+        ops.linear(through_copy, xd, wd)
+        assert torch.equal(through_copy.cpu(), out.cpu())
+        key = wd.data_ptr()
+        assert key in ops._slabs
+        del wd
         import gc
         gc.collect()
-        assert key not in ops._tiled, "the tiled copy outlived its matrix"
+        assert key not in ops._slabs, "the copy outlived its matrix"
 
 
 @pytest.mark.parametrize("M", [17, 33, 64, 100, 128])
