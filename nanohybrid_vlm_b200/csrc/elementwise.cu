@@ -93,7 +93,15 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bf16x8_kernel(
     const __nv_bfloat16* __restrict__ w, const int* __restrict__ rows, int width8, float eps, int write_residual,
     float weight_offset) {
   __shared__ float red[33];
-  pdl_prologue();
+  // the norm's weight is no kernel's output: fetch it while the kernel before this one is still running
+  pdl_launch_dependents();
+  uint4 wv[RN_CHUNKS];
+#pragma unroll
+  for (int i = 0; i < RN_CHUNKS; ++i) {
+    const int c = threadIdx.x + i * RN_THREADS;
+    wv[i] = c < width8 ? reinterpret_cast<const uint4*>(w)[c] : make_uint4(0, 0, 0, 0);
+  }
+  pdl_wait();
   const int r = blockIdx.x;
   const size_t src = (size_t)(rows ? rows[r] : r) * width8;
   const uint4* x4 = reinterpret_cast<const uint4*>(x) + src;
@@ -128,13 +136,11 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bf16x8_kernel(
   const float total = block_sum(ss, red);
   const float rstd = 1.0f / sqrtf(total / (float)(width8 * 8) + eps);
   uint4* out4 = reinterpret_cast<uint4*>(out) + (size_t)r * width8;
-  const uint4* w4 = reinterpret_cast<const uint4*>(w);
 #pragma unroll
   for (int i = 0; i < RN_CHUNKS; ++i) {
     const int c = threadIdx.x + i * RN_THREADS;
     if (c < width8) {
-      const uint4 wv = w4[c];
-      const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(&wv);
+      const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(&wv[i]);
       uint4 ov;
       __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&ov);
 #pragma unroll
