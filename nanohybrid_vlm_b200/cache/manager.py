@@ -202,6 +202,14 @@ class CacheManager:
     def allocate(self, req_id, num_tokens: int) -> None:
         """Make sure tokens [0, num_tokens) of the request have pages in every group; a new request also
         gets its state slot.  Raises :class:`OutOfPages` and changes nothing if any group falls short."""
+        req = self._requests.get(req_id)
+        if req is not None:
+            # the usual decode step: the pages the request holds already cover the new token
+            total = -(-num_tokens // self.page_size)
+            if all(len(t) >= total for t in req.tables):
+                if num_tokens > req.num_tokens:
+                    req.num_tokens = num_tokens
+                return
         if not self.can_allocate(req_id, num_tokens):
             raise OutOfPages(f"request {req_id!r}: no room for {num_tokens} tokens "
                              f"(free pages per group: {[p.num_free for p in self.pools]})")

@@ -71,6 +71,7 @@ class BatchBuilder:
         self.page_size = cache_manager.page_size
         self.n_groups = len(cache_manager.groups)
         self.max_tokens, self.max_seqs, self.max_pages = max_tokens, max_seqs, max_pages_per_seq
+        self._layouts: dict = {}
         cap = self._layout(max_tokens, max_seqs, max_tokens, max_pages_per_seq)[1]
         self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self._np = self._host.numpy()
@@ -80,6 +81,10 @@ class BatchBuilder:
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
 
     def _layout(self, T: int, S: int, R: int, width: int):
+        key = (T, S, R, width)
+        cached = self._layouts.get(key)
+        if cached is not None:
+            return cached
         off, sections = 0, {}
         for name, n in (("seeds", 2 * R), ("temperatures", R), ("sample_positions", R), ("token_ids", T),
                         ("positions", T), ("cu_q", S + 1), ("kv_len", S), ("q_start", S),
@@ -91,13 +96,15 @@ class BatchBuilder:
             off += _align(T)
             sections[f"tables{g}"] = (off, S * width)
             off += _align(S * width)
+        self._layouts[key] = (sections, off)
         return sections, off
 
     def build(self, items: list[StepItem], table_width: int | None = None, sampling=None,
-              pad_to: int | None = None) -> StepBatch:
+              pad_to: int | None = None, views: bool = True) -> StepBatch | None:
         """``sampling``: one (temperature, seed, position of the token being chosen) per wanted row.
         ``pad_to``: for a batch of single tokens, fill up to this many requests with idle entries (one
-        token that is stored nowhere and reads no page), so that the batch has a fixed shape."""
+        token that is stored nowhere and reads no page), so that the batch has a fixed shape.
+        ``views`` False: only fill and copy the arrays (for the replay of a captured step) and return None."""
         n_real = len(items)
         pad = 0 if pad_to is None else pad_to - n_real
         if pad < 0 or (pad_to is not None and any(len(it.tokens) != 1 or it.want != [0] for it in items)):
@@ -147,9 +154,6 @@ class BatchBuilder:
             if self.cm.num_tokens(it.req_id) < end:
                 raise RuntimeError(f"request {it.req_id!r}: pages cover {self.cm.num_tokens(it.req_id)} tokens, "
                                    f"the step needs {end}")
-            tok[t:t + n] = it.tokens
-            p = np.arange(it.start, end, dtype=np.int32)
-            pos[t:t + n] = p
             cu[s + 1] = t + n
             kvl[s], qs[s] = end, it.start
             slot = self.cm.state_slot(it.req_id)
@@ -159,11 +163,25 @@ class BatchBuilder:
                     raise ValueError(f"request {it.req_id!r}: wanted place {w} is not among its {n} tokens")
                 rows[r] = t + w
                 r += 1
-            for g in range(self.n_groups):
-                table = np.asarray(self.cm.block_table(it.req_id, g), dtype=np.int32)
-                table_views[g][s, :min(len(table), width)] = table[:width]
-                pages = table[p // ps]
-                slot_views[g][t:t + n] = np.where(pages >= 0, pages * ps + p % ps, -1)
+            if n == 1:
+                # a decoded token: scalars instead of arrays (this is the hot path of every decode step)
+                tok[t] = it.tokens[0]
+                pos[t] = it.start
+                for g in range(self.n_groups):
+                    table = self.cm.block_table(it.req_id, g)
+                    k = min(len(table), width)
+                    table_views[g][s, :k] = table[:k]
+                    page = table[it.start // ps]
+                    slot_views[g][t] = page * ps + it.start % ps if page >= 0 else -1
+            else:
+                tok[t:t + n] = it.tokens
+                p = np.arange(it.start, end, dtype=np.int32)
+                pos[t:t + n] = p
+                for g in range(self.n_groups):
+                    table = np.asarray(self.cm.block_table(it.req_id, g), dtype=np.int32)
+                    table_views[g][s, :min(len(table), width)] = table[:width]
+                    pages = table[p // ps]
+                    slot_views[g][t:t + n] = np.where(pages >= 0, pages * ps + p % ps, -1)
             t += n
         for s in range(n_real, S):          # idle entries
             tok[t], pos[t] = 0, 0
@@ -180,6 +198,8 @@ class BatchBuilder:
         if self._copied is not None:
             self._copied.record()
         self.bytes_last_copy = total * 4
+        if not views:           # a replayed graph reads the arrays where they lie; nobody needs the views
+            return None
 
         def dev(name):
             o, n = sec[name]

@@ -131,7 +131,7 @@ class ModelRunner:
         if bucket not in self._graphs:
             self._capture(bucket)
         graph, tokens, launches = self._graphs[bucket]
-        self.builder.build(items, table_width=self.max_pages_per_seq, sampling=sampling, pad_to=bucket)
+        self.builder.build(items, table_width=self.max_pages_per_seq, sampling=sampling, pad_to=bucket, views=False)
         graph.replay()
         library.LAUNCHES += launches     # the kernels that the replay launched
         return tokens[:len(items)].tolist()
