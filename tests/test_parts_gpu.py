@@ -1,8 +1,8 @@
 """Each part of a layer alone against the plain implementation's function for it, and a toy
 architecture, defined here, whose layers mix a mixer with fixed-size state of its own with attention,
 run one layer twice and let a run read another run's cache; another with a windowed layer; a third with a
-feed-forward that routes tokens to experts and a learnt position table: each registered, built from random
-weights and stepped without a change to the framework's files."""
+feed-forward that routes tokens to experts, a learnt position table, another norm and another arrangement of a
+layer's parts: each registered, built from random weights and stepped without a change to the framework's files."""
 import json
 
 import numpy as np
@@ -453,8 +453,8 @@ def register_routed_toy():
     """A feed-forward that routes every token to one of its experts, and a position encoding with a learnt table
     that is added to the embedded tokens (the attention layers then rotate nothing): both defined here."""
     from nanohybrid_vlm_b200.config import ModelConfig, register_architecture
-    from nanohybrid_vlm_b200.parts import (FEED_FORWARDS, POSITIONS, FeedForward, LayerRun, LayerSpec, ModelSpec,
-                                           ParamDecl, PartUse, PositionEncoding, part)
+    from nanohybrid_vlm_b200.parts import (BLOCKS, FEED_FORWARDS, NORMS, POSITIONS, Block, FeedForward, LayerRun,
+                                           LayerSpec, ModelSpec, Norm, ParamDecl, PartUse, PositionEncoding, part)
 
     class TopOneExperts(FeedForward):
         def __init__(self, spec, env):
@@ -483,8 +483,45 @@ def register_routed_toy():
         def add_to_embeddings(self, h, batch):
             return (h.float() + self.w_weight.float()[batch.positions.long()]).to(h.dtype)
 
+    class MeanCentredNorm(Norm):
+        """A LayerNorm without bias: mean and variance over the row, times a weight (another norm than the
+        engine's own), with the residual add that the block arrangement asks of every norm."""
+
+        def params(self):
+            return [ParamDecl("weight", (int(self.spec["width"]),), init="norm")]
+
+        def _norm(self, s):
+            s = s - s.mean(-1, keepdim=True)
+            return s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + float(self.spec["eps"])) * self.w_weight.float()
+
+        def forward(self, x):
+            return self._norm(x.float()).to(x.dtype)
+
+        def forward_add(self, x, residual):
+            s = x.float() + residual.float()
+            residual.copy_(s.to(residual.dtype))
+            return self._norm(s).to(x.dtype)
+
+        def forward_add_rows(self, x, residual, rows):
+            r = rows.long()
+            return self._norm(x[r].float() + residual[r].float()).to(x.dtype)
+
+    class ParallelBlock(Block):
+        """Another arrangement of the same four parts: mixer and feed-forward both read one norm of the stream
+        and their outputs are added together (the second norm of the layer goes unused, with its tensor)."""
+
+        def forward(self, hidden, residual, batch, cache):
+            if residual is None:
+                residual = hidden
+                x = self.mixer_norm.forward(hidden)
+            else:
+                x = self.mixer_norm.forward_add(hidden, residual)
+            return self.mixer.forward(x, batch, cache) + self.ffn.forward(x, batch), residual
+
     FEED_FORWARDS.register("top_one_experts", TopOneExperts, replace=True)
     POSITIONS.register("learnt", LearntPositions, replace=True)
+    NORMS.register("mean_centred", MeanCentredNorm, replace=True)
+    BLOCKS.register("parallel", ParallelBlock, replace=True)
 
     def parse(raw):
         cfg = ModelConfig(architecture="ToyRoutedLM", model_type=raw["model_type"], vocab_size=raw["vocab_size"],
@@ -502,16 +539,19 @@ def register_routed_toy():
         experts = part("top_one_experts", num_experts=raw["num_experts"], expert_size=raw["expert_size"])
         dense = part("swiglu", intermediate_size=raw["intermediate_size"])
 
-        def layer(i, ffn):
-            return LayerSpec(part("prenorm_residual"), PartUse(attn, f"layers.{i}.attn."), PartUse(norm, f"layers.{i}.norm1."),
-                             PartUse(ffn, f"layers.{i}.ffn."), PartUse(norm, f"layers.{i}.norm2."))
+        centred = part("mean_centred", width=H, eps=raw["rms_norm_eps"])
+
+        def layer(i, ffn, block="prenorm_residual", layer_norm=norm):
+            return LayerSpec(part(block), PartUse(attn, f"layers.{i}.attn."), PartUse(layer_norm, f"layers.{i}.norm1."),
+                             PartUse(ffn, f"layers.{i}.ffn."), PartUse(layer_norm, f"layers.{i}.norm2."))
 
         return ModelSpec(architecture="ToyRoutedLM", hidden_size=H, vocab_size=raw["vocab_size"],
                          max_position=raw["max_position_embeddings"],
                          embedding=PartUse(part("token_embedding", vocab_size=raw["vocab_size"]), "embed."),
                          positions=(PartUse(part("learnt", max_position=raw["max_position_embeddings"]), "positions."),),
-                         layers=(layer(0, experts), layer(1, dense)),   # a routed and a dense feed-forward
-                         order=(LayerRun(0), LayerRun(1)),
+                         # a routed and a dense feed-forward; then a layer in another arrangement with another norm
+                         layers=(layer(0, experts), layer(1, dense), layer(2, dense, "parallel", centred)),
+                         order=(LayerRun(0), LayerRun(1), LayerRun(2)),
                          final_norm=PartUse(norm, "final_norm."),
                          head=PartUse(part("lm_head", vocab_size=raw["vocab_size"], tied=False), "head."))
 
@@ -547,15 +587,24 @@ def routed_plain_logits(w, tokens):
             h = torch.stack(rows)
         else:
             h = plain.swiglu_mlp(x, w, p + "ffn.")
+    # layer 2: the parallel arrangement behind a mean-centred norm
+    residual = h + residual
+    c = residual - residual.mean(-1, keepdim=True)
+    x = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * w["layers.2.norm1.weight"]
+    q = plain.linear(x, w["layers.2.attn.q_proj.weight"]).view(T, nq, d)
+    k = plain.linear(x, w["layers.2.attn.k_proj.weight"]).view(T, nkv, d)
+    v = plain.linear(x, w["layers.2.attn.v_proj.weight"]).view(T, nkv, d)
+    o = plain.causal_attention(q, k, v, d ** -0.5)
+    h = plain.linear(o.reshape(T, nq * d), w["layers.2.attn.o_proj.weight"]) + plain.swiglu_mlp(x, w, "layers.2.ffn.")
     x, _ = plain.add_rms_norm(h, residual, w["final_norm.weight"], eps)
     return plain.linear(x, w["head.weight"])
 
 
-def test_a_routed_feed_forward_and_a_learnt_position_table_register_build_and_step(tmp_path):
+def test_routing_learnt_positions_another_norm_and_another_block_register_build_and_step(tmp_path):
     from safetensors.torch import load_file
     from nanohybrid_vlm_b200.config import ARCHITECTURES, Config
     from nanohybrid_vlm_b200.engine import ModelRunner, StepItem
-    from nanohybrid_vlm_b200.parts import FEED_FORWARDS, POSITIONS
+    from nanohybrid_vlm_b200.parts import BLOCKS, FEED_FORWARDS, NORMS, POSITIONS
     from nanohybrid_vlm_b200.weights import write_random_model
     register_routed_toy()
     try:
@@ -592,3 +641,5 @@ def test_a_routed_feed_forward_and_a_learnt_position_table_register_build_and_st
         ARCHITECTURES.unregister("ToyRoutedLM")
         FEED_FORWARDS.unregister("top_one_experts")
         POSITIONS.unregister("learnt")
+        NORMS.unregister("mean_centred")
+        BLOCKS.unregister("parallel")
