@@ -22,12 +22,24 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32
   }
 }
 
-__global__ void __launch_bounds__(1024) sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
-                                                      int ld, const float* __restrict__ temperatures,
-                                                      const unsigned long long* __restrict__ seeds,
-                                                      const int* __restrict__ positions, int vocab) {
-  __shared__ float best_v[32];
-  __shared__ int best_i[32];
+// Scores are compared as 64-bit keys: the score's bits made order-preserving in the high word, the complement of
+// the index in the low word, so that the largest key is the best score and, among equal scores, the lowest
+// index (what a sequential argmax gives).
+__device__ __forceinline__ unsigned long long score_key(float s, int i) {
+  const uint32_t b = __float_as_uint(s);
+  const uint32_t ordered = b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+  return ((unsigned long long)ordered << 32) | (uint32_t)(~(uint32_t)i);
+}
+
+// A row is cut into gridDim.y pieces, one block each; the blocks meet at the row's slot of `best` (atomic
+// maximum of the keys) and count their arrival; the block that arrives last writes the row's token and
+// returns slot and counter to zero for the next launch.  No block waits for another.
+__global__ void __launch_bounds__(256) sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
+                                                     int ld, const float* __restrict__ temperatures,
+                                                     const unsigned long long* __restrict__ seeds,
+                                                     const int* __restrict__ positions, int vocab,
+                                                     unsigned long long* __restrict__ best, int* __restrict__ arrived) {
+  __shared__ unsigned long long warp_best[8];
   pdl_prologue();
   const int row = blockIdx.x;
   const float* lg = logits + (size_t)row * ld;
@@ -35,55 +47,69 @@ __global__ void __launch_bounds__(1024) sample_kernel(int* __restrict__ out, con
   const unsigned long long seed = seeds[row];
   const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
   const uint32_t pos = (uint32_t)positions[row];
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
   const int n_groups = (vocab + 3) >> 2;
-  for (int gidx = threadIdx.x; gidx < n_groups; gidx += blockDim.x) {
+  const int per = (n_groups + gridDim.y - 1) / gridDim.y;
+  const int g_end = min(n_groups, ((int)blockIdx.y + 1) * per);
+  const bool vec = (ld & 3) == 0 && ((uintptr_t)logits & 15) == 0;
+  unsigned long long key = 0;
+  for (int gidx = blockIdx.y * per + threadIdx.x; gidx < g_end; gidx += blockDim.x) {
     uint32_t c[4] = {(uint32_t)gidx, pos, 0u, 0u};
     if (temp > 0.f) philox4x32_10(c, k0, k1);
+    float v[4];
+    if (vec && gidx * 4 + 3 < vocab) {
+      const float4 f = *reinterpret_cast<const float4*>(lg + gidx * 4);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] = gidx * 4 + k < vocab ? lg[gidx * 4 + k] : -INFINITY;
+    }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int i = gidx * 4 + k;
       if (i >= vocab) break;
-      float s = lg[i];
+      float s = v[k];
       if (temp > 0.f) {
         const float u = ((float)(c[k] >> 9) + 0.5f) * (1.0f / 8388608.0f);
         const float noise = fmaxf(-logf(u), 1e-10f);
         s = s / temp - logf(noise);
       }
-      if (s > bv || (s == bv && i < bi)) { bv = s; bi = i; }
+      const unsigned long long kk = score_key(s, i);
+      key = kk > key ? kk : key;
     }
   }
-  // lowest index among equal scores, as a sequential argmax gives
   for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+    key = other > key ? other : key;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+  if (lane == 0) warp_best[warp] = key;
   __syncthreads();
-  if (warp == 0) {
-    const int nw = blockDim.x >> 5;
-    bv = lane < nw ? best_v[lane] : -INFINITY;
-    bi = lane < nw ? best_i[lane] : 0x7fffffff;
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) key = warp_best[w] > key ? warp_best[w] : key;
+    atomicMax(best + row, key);
+    __threadfence();
+    if (atomicAdd(arrived + row, 1) == (int)gridDim.y - 1) {
+      __threadfence();
+      const unsigned long long win = atomicExch(best + row, 0ull);     // read and return to zero
+      const uint32_t idx = ~(uint32_t)win;
+      out[row] = win == 0ull || idx >= (uint32_t)vocab ? 0 : (int)idx;
+      arrived[row] = 0;
     }
-    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
   }
 }
 
+// best [n_rows] 64-bit words and arrived [n_rows] ints, all zero (the kernel leaves them zero).
 NHV_API int nhv_sample(int* out, const float* logits, int ld, const float* temperatures,
                        const unsigned long long* seeds, const int* positions, int n_rows, int vocab,
-                       cudaStream_t stream) {
+                       unsigned long long* best, int* arrived, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  NHV_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab, "sample: bad sizes");
-  int threads = 128;
-  while (threads < 1024 && threads * 16 < vocab) threads <<= 1;
-  nhv_launch(sample_kernel, n_rows, threads, 0, stream, out, logits, ld, temperatures, seeds, positions, vocab);
+  NHV_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab && best && arrived, "sample: bad arguments");
+  // pieces of about 8,192 scores, but no more blocks than a few per SM
+  int pieces = (vocab + 8191) / 8192;
+  const int room = 148 * 4 / n_rows;
+  if (pieces > room) pieces = room < 1 ? 1 : room;
+  nhv_launch(sample_kernel, dim3(n_rows, pieces), 256, 0, stream, out, logits, ld, temperatures, seeds, positions, vocab,
+             best, arrived);
   NHV_CHECK_LAUNCH("sample");
   return 0;
 }

@@ -485,5 +485,18 @@ def sample(out, logits, temperatures, seeds, positions) -> None:
     _need_cuda(out, logits, temperatures, seeds, positions)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
     assert temperatures.dtype == torch.float32 and seeds.dtype == torch.int64 and positions.dtype == torch.int32
+    rows = logits.shape[0]
+    st = _sampler_scratch.get(logits.device)
+    if st is None or st[0].numel() < rows:
+        # where the blocks that share a row meet: zero, and left zero by every launch
+        n = max(rows, 512)
+        if st is not None:
+            _sampler_retired.append(st)      # a captured step may still point at the smaller ones
+        st = _sampler_scratch[logits.device] = (torch.zeros(n, dtype=torch.int64, device=logits.device),
+                                                torch.zeros(n, dtype=torch.int32, device=logits.device))
     call("nhv_sample", out.data_ptr(), logits.data_ptr(), logits.stride(0), temperatures.data_ptr(), seeds.data_ptr(),
-         positions.data_ptr(), logits.shape[0], logits.shape[1], stream_ptr())
+         positions.data_ptr(), rows, logits.shape[1], st[0].data_ptr(), st[1].data_ptr(), stream_ptr())
+
+
+_sampler_scratch: dict = {}
+_sampler_retired: list = []
