@@ -40,6 +40,8 @@ class _Request:
     released: list[int]                     # per group: logical pages [0, released) were given back
     state_slot: int | None = None
     num_tokens: int = 0                     # tokens that have pages
+    hashed: int = 0                         # leading full pages whose content hash has been taken (prefix reuse)
+    chain: int = 0                          # the hash of the last of them (0: none yet)
 
 
 class CacheManager:
@@ -58,6 +60,7 @@ class CacheManager:
         if enable_prefix_cache and not self.prefix_cache_possible(self.groups, num_state_slots):
             raise ValueError("prefix reuse needs groups that keep every key and a model without per-request state")
         self.prefix_cache = enable_prefix_cache
+        self.has_windows = any(g.window is not None for g in self.groups)
         # per group: hash -> page, and for every page that carries a hash: (hash, its token ids)
         self._by_hash: list[dict[int, int]] = [{} for _ in self.groups]
         self._page_info: list[dict[int, tuple[int, tuple]]] = [{} for _ in self.groups]
@@ -123,9 +126,13 @@ class CacheManager:
             for page in pages:
                 self.pools[g].share(page)
             req.tables[g].extend(pages)
-        self.prefix_hits += len(hits[0]) if hits else 0
+        n_hit = len(hits[0]) if hits else 0
+        self.prefix_hits += n_hit
+        if n_hit:
+            req.hashed = n_hit
+            req.chain = self._page_info[0][hits[0][-1]][0]
         self.allocate(req_id, len(token_ids))
-        return (len(hits[0]) if hits else 0) * self.page_size
+        return n_hit * self.page_size
 
     def commit(self, req_id, token_ids, num_computed: int) -> None:
         """After a step: the request's pages that are now full and computed get their hashes, so that later
@@ -137,22 +144,20 @@ class CacheManager:
             return
         ps = self.page_size
         full = min(num_computed, len(token_ids)) // ps
-        for g in range(len(self.groups)):
-            table = req.tables[g]
-            # the chain continues from the last page of this request that already has a hash
-            i = 0
-            prev = 0
-            while i < full and table[i] in self._page_info[g]:
-                prev = self._page_info[g][table[i]][0]
-                i += 1
-            for j in range(i, full):
-                chunk = tuple(token_ids[j * ps:(j + 1) * ps])
-                prev = self._page_hash(prev, chunk)
-                page = table[j]
+        if full <= req.hashed:
+            return                                  # the usual step: no page has filled up
+        # every group holds the same tokens, so one chain of hashes serves all of them
+        prev = req.chain
+        for j in range(req.hashed, full):
+            chunk = tuple(token_ids[j * ps:(j + 1) * ps])
+            prev = self._page_hash(prev, chunk)
+            for g in range(len(self.groups)):
+                page = req.tables[g][j]
                 if prev not in self._by_hash[g]:
                     self._by_hash[g][prev] = page
                     self._page_info[g][page] = (prev, chunk)
                 # else the same contents already sit on another page: this one stays anonymous
+        req.hashed, req.chain = full, prev
 
     def _forget(self, g: int, pages) -> None:
         """Pages that are handed out for new contents lose their hashes."""
@@ -187,6 +192,17 @@ class CacheManager:
             return False
         if req_id not in self._requests and self.slots is not None and not self.slots.can_allocate():
             return False
+        return True
+
+    def covers(self, req_id, num_tokens: int) -> bool:
+        """True if the request's pages already cover tokens [0, num_tokens) in every group (the usual decode step)."""
+        req = self._requests.get(req_id)
+        if req is None:
+            return False
+        total = -(-num_tokens // self.page_size)
+        for t in req.tables:
+            if len(t) < total:
+                return False
         return True
 
     def block_table(self, req_id, group: int = 0) -> list[int]:

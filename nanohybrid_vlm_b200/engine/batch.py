@@ -146,7 +146,36 @@ class BatchBuilder:
                 temps[i], seeds[i], spos[i] = temp, seed, p
         t = r = 0
         cu[0] = 0
-        for s, it in enumerate(items):
+        if n_real and all(len(it.tokens) == 1 and it.want == [0] for it in items):
+            # a step of decoded tokens, each wanting its logits: the per-request numbers as whole arrays, the
+            # tables row by row
+            requests = self.cm._requests
+            starts, slots_state, firsts = [], [], []
+            for s, it in enumerate(items):
+                req = requests[it.req_id]
+                start = it.start
+                if req.num_tokens <= start:
+                    raise RuntimeError(f"request {it.req_id!r}: pages cover {req.num_tokens} tokens, the step needs {start + 1}")
+                starts.append(start)
+                firsts.append(it.tokens[0])
+                slots_state.append(-1 if req.state_slot is None else req.state_slot)
+                lp, off = divmod(start, ps)
+                for g in range(self.n_groups):
+                    table = req.tables[g]
+                    k = len(table) if len(table) < width else width
+                    table_views[g][s, :k] = table[:k]
+                    page = table[lp]
+                    slot_views[g][s] = page * ps + off if page >= 0 else -1
+            n = n_real
+            tok[:n], pos[:n], qs[:n], st[:n] = firsts, starts, starts, slots_state
+            kvl[:n] = pos[:n] + 1
+            cu[1:n + 1] = np.arange(1, n + 1, dtype=np.int32)
+            rows[:n] = cu[:n]
+            t = r = n
+            items_loop = ()
+        else:
+            items_loop = items
+        for s, it in enumerate(items_loop):
             n = len(it.tokens)
             if n == 0:
                 raise ValueError(f"request {it.req_id!r} brings no token")

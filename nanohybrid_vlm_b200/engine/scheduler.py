@@ -76,7 +76,8 @@ class Scheduler:
             for seq in list(self.running):
                 if seq.status != SequenceStatus.RUNNING or budget == 0 or len(plan.seqs) >= self.max_num_seqs:
                     continue
-                while not self.cache.can_allocate(seq.seq_id, len(seq)):
+                n = len(seq)
+                while not (self.cache.covers(seq.seq_id, n) or self.cache.can_allocate(seq.seq_id, n)):
                     victim = self._pick_victim(scheduled, exclude=seq)
                     if victim is None:
                         victim = seq
@@ -85,7 +86,7 @@ class Scheduler:
                         break
                 if seq.status != SequenceStatus.RUNNING:
                     continue
-                self.cache.allocate(seq.seq_id, len(seq))
+                self.cache.allocate(seq.seq_id, n)
                 seq.num_scheduled_tokens = 1
                 plan.seqs.append(seq)
                 scheduled.add(seq.seq_id)
@@ -146,9 +147,11 @@ class Scheduler:
         for seq, token in zip(seqs, token_ids):
             seq.num_cached_tokens += seq.num_scheduled_tokens
             seq.num_scheduled_tokens = 0
-            self.cache.commit(seq.seq_id, seq.token_ids, seq.num_cached_tokens)
+            if self.cache.prefix_cache:
+                self.cache.commit(seq.seq_id, seq.token_ids, seq.num_cached_tokens)
             if seq.num_cached_tokens < len(seq):
-                self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
+                if self.cache.has_windows:
+                    self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
                 continue
             if token is None:
                 raise RuntimeError(f"request {seq.seq_id}: its last token was computed but no token was chosen")
@@ -159,5 +162,5 @@ class Scheduler:
                 seq.status = SequenceStatus.FINISHED
                 self.cache.free(seq.seq_id)
                 self.running.remove(seq)
-            else:
+            elif self.cache.has_windows:
                 self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
