@@ -22,7 +22,7 @@ state: a window or a state cannot be rebuilt from shared pages.
 from __future__ import annotations
 
 import hashlib
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import numpy as np
 

@@ -9,7 +9,7 @@ is one mixed batch: prompt portions beside decoded tokens.
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from time import perf_counter
 
 from ..config import Config

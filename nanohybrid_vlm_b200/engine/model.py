@@ -11,7 +11,7 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, CacheView, FixedStateNeed, PagedKVNeed, Part
+from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, FixedStateNeed, PagedKVNeed, Part
 from ..parts.embedding import LMHead, TokenEmbedding
 from ..parts.spec import ModelSpec, ParamDecl, PartUse, Source
 

@@ -10,8 +10,6 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-import torch
-
 from ..config.model_config import ConfigError, ModelConfig, parse_dtype, take
 from ..config.registry import register_architecture
 from ..parts.spec import LayerRun, LayerSpec, ModelSpec, PartUse, part

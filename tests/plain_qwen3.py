@@ -19,7 +19,6 @@ reference rounds.  Matrix products accumulate in float32 and round once.
 from __future__ import annotations
 
 import json
-import math
 import os
 
 import numpy as np

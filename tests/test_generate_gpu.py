@@ -3,7 +3,6 @@ decoding, the first tokens of a sequence, prompts cut into portions beside decod
 so small that requests are preempted and recomputed, seeded temperature sampling."""
 import numpy as np
 import pytest
-import torch
 
 import plain_qwen3 as plain
 from conftest import TINY

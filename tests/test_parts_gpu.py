@@ -3,8 +3,6 @@ architecture, defined here, whose layers mix a mixer with fixed-size state of it
 run one layer twice and let a run read another run's cache; another with a windowed layer; a third with a
 feed-forward that routes tokens to experts, a learnt position table, another norm and another arrangement of a
 layer's parts: each registered, built from random weights and stepped without a change to the framework's files."""
-import json
-
 import numpy as np
 import pytest
 import torch

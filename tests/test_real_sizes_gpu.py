@@ -4,7 +4,6 @@ that serving uses at full size (streaming GEMMs with tensor maps, tensor-core at
 against the plain implementation, in 32-bit and in bfloat16."""
 import numpy as np
 import pytest
-import torch
 
 import trace_tools as tt
 

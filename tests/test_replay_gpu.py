@@ -4,7 +4,6 @@ with other requests in a pool so small that pages are used again; in 32-bit and 
 on two tiny configurations."""
 import numpy as np
 import pytest
-import torch
 
 import trace_tools as tt
 from conftest import TINY, TINY_C

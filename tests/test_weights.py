@@ -3,7 +3,6 @@ import os
 
 import pytest
 import torch
-from safetensors import safe_open
 from safetensors.torch import load_file, save_file
 
 from conftest import TINY_A, TINY_B
