@@ -206,3 +206,50 @@ def test_prefix_reuse_random_orders(seed):
         cm.free(rid)
     cm.check()
     assert cm.pools[0].num_free == 40 and cm.prefix_hits > 0
+
+
+def test_a_page_is_hashed_once_even_when_its_contents_sit_elsewhere(monkeypatch):
+    """Committing after every step costs a hash only when a page fills up: also for a request whose full page
+    repeats contents that another page already holds (that page stays anonymous), and for a request that began
+    behind shared pages (its chain continues from the last of them)."""
+    cm = CacheManager([GroupSpec(None)], page_size=4, num_pages=16, enable_prefix_cache=True)
+    calls = []
+    real = CacheManager._page_hash
+    monkeypatch.setattr(CacheManager, "_page_hash", staticmethod(lambda prev, toks: calls.append(tuple(toks)) or real(prev, toks)))
+    a = list(range(10))
+    cm.admit("a", a)
+    calls.clear()                                               # (admission hashes too: it looks pages up)
+    cm.commit("a", a, 10)                                       # two full pages
+    assert calls == [tuple(a[:4]), tuple(a[4:8])]
+    cm.commit("a", a, 10)
+    assert len(calls) == 2                                      # nothing new: nothing hashed
+    cm.free("a")                                                # the pages are free but still findable
+    b = a[:8] + [50, 51]                                        # b: first page shared, second (the same contents
+    assert cm.admit("b", b[:8]) == 4                            # as a's, whose page still holds that hash) its own:
+    calls.clear()                                               # the last page of what is admitted is never shared
+    cm.commit("b", b[:8], 8)
+    assert calls == [tuple(a[4:8])]                             # one new page: hashed once (and left anonymous)
+    for n in range(9, 11):                                      # decode steps inside the third page: no hashing
+        cm.allocate("b", n)
+        cm.commit("b", b[:n], n)
+    assert len(calls) == 1
+    b += [52, 53]
+    cm.allocate("b", 12)
+    cm.commit("b", b, 12)                                       # the third page is full now
+    assert calls[1:] == [tuple(b[8:12])]
+    # and the chain through the anonymous page is the right one: a request with b's tokens finds pages 1 and 3
+    probe = cm._probe(b + [0])
+    assert len(probe[0]) == 3
+    cm.check()
+
+
+def test_covers_tells_whether_pages_are_needed():
+    cm = CacheManager([GroupSpec(None), GroupSpec(6)], page_size=4, num_pages=[8, 8])
+    assert not cm.covers("x", 1)
+    cm.allocate("x", 5)
+    assert cm.covers("x", 8) and not cm.covers("x", 9)
+    cm.allocate("x", 7)                                         # no page needed: only the count moves
+    assert cm.num_tokens("x") == 7 and cm.block_table("x", 0) == [0, 1]
+    cm.allocate("x", 9)
+    assert cm.block_table("x", 0) == [0, 1, 2] and cm.covers("x", 12)
+    cm.check()
