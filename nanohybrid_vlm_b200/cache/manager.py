@@ -40,6 +40,7 @@ class _Request:
     released: list[int]                     # per group: logical pages [0, released) were given back
     state_slot: int | None = None
     num_tokens: int = 0                     # tokens that have pages
+    serial: int = 0                         # a number no other request record of this manager ever had
     hashed: int = 0                         # leading full pages whose content hash has been taken (prefix reuse)
     chain: int = 0                          # the hash of the last of them (0: none yet)
 
@@ -61,6 +62,7 @@ class CacheManager:
             raise ValueError("prefix reuse needs groups that keep every key and a model without per-request state")
         self.prefix_cache = enable_prefix_cache
         self.has_windows = any(g.window is not None for g in self.groups)
+        self._serial = 0
         # per group: hash -> page, and for every page that carries a hash: (hash, its token ids)
         self._by_hash: list[dict[int, int]] = [{} for _ in self.groups]
         self._page_info: list[dict[int, tuple[int, tuple]]] = [{} for _ in self.groups]
@@ -122,6 +124,8 @@ class CacheManager:
                              f"(free pages per group: {[p.num_free for p in self.pools]})")
         hits = self._probe(token_ids)
         req = self._requests[req_id] = _Request([[] for _ in self.groups], [0] * len(self.groups), None)
+        self._serial += 1
+        req.serial = self._serial
         for g, pages in enumerate(hits):
             for page in pages:
                 self.pools[g].share(page)
@@ -233,6 +237,8 @@ class CacheManager:
         if req is None:
             slot = self.slots.allocate() if self.slots is not None else None
             req = self._requests[req_id] = _Request([[] for _ in self.groups], [0] * len(self.groups), slot)
+            self._serial += 1
+            req.serial = self._serial
         for g, n in enumerate(self.pages_needed(req_id, num_tokens)):
             fresh = self.pools[g].allocate(n)
             if self.prefix_cache:

@@ -72,6 +72,8 @@ class BatchBuilder:
         self.n_groups = len(cache_manager.groups)
         self.max_tokens, self.max_seqs, self.max_pages = max_tokens, max_seqs, max_pages_per_seq
         self._layouts: dict = {}
+        self._table_rows = None          # (layout, per row (request, table length)) of the last all-decode step
+        self._windows = any(g.window is not None for g in cache_manager.groups)
         cap = self._layout(max_tokens, max_seqs, max_tokens, max_pages_per_seq)[1]
         self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self._np = self._host.numpy()
@@ -133,8 +135,18 @@ class BatchBuilder:
         cu, kvl, qs, st, rows = view("cu_q"), view("kv_len"), view("q_start"), view("state_slots"), view("logit_rows")
         slot_views = [view(f"slots{g}") for g in range(self.n_groups)]
         table_views = [view(f"tables{g}").reshape(S, width) for g in range(self.n_groups)]
-        for tv in table_views:
-            tv.fill(-1)
+        # In a run of decode steps over the same requests the tables change only when a request gets a page.  The
+        # host buffer still holds the last step's rows if the arrays lie where they lay then: a row is written
+        # again only if its request or the length of its table differs (a group with a window rewrites always:
+        # pages given back change entries without changing the length).
+        layout_key = (T, S, R, width)
+        decode_only = n_real > 0 and all(len(it.tokens) == 1 and it.want == [0] for it in items)
+        keep = decode_only and self._table_rows is not None and self._table_rows[0] == layout_key
+        old_rows = self._table_rows[1] if keep else None
+        new_rows = [None] * S if decode_only else None
+        if not keep:
+            for tv in table_views:
+                tv.fill(-1)
         if sampling is not None:
             if len(sampling) != R - pad:
                 raise ValueError("one (temperature, seed, position) per wanted row is needed")
@@ -146,7 +158,7 @@ class BatchBuilder:
                 temps[i], seeds[i], spos[i] = temp, seed, p
         t = r = 0
         cu[0] = 0
-        if n_real and all(len(it.tokens) == 1 and it.want == [0] for it in items):
+        if decode_only:
             # a step of decoded tokens, each wanting its logits: the per-request numbers as whole arrays, the
             # tables row by row
             requests = self.cm._requests
@@ -160,10 +172,15 @@ class BatchBuilder:
                 firsts.append(it.tokens[0])
                 slots_state.append(-1 if req.state_slot is None else req.state_slot)
                 lp, off = divmod(start, ps)
+                stamp = (req.serial, len(req.tables[0]))     # a request that was given up and came back is another record
+                new_rows[s] = stamp
+                same = keep and not self._windows and old_rows[s] == stamp
                 for g in range(self.n_groups):
                     table = req.tables[g]
-                    k = len(table) if len(table) < width else width
-                    table_views[g][s, :k] = table[:k]
+                    if not same:
+                        k = len(table) if len(table) < width else width
+                        table_views[g][s, :k] = table[:k]
+                        table_views[g][s, k:] = -1
                     page = table[lp]
                     slot_views[g][s] = page * ps + off if page >= 0 else -1
             n = n_real
@@ -213,6 +230,9 @@ class BatchBuilder:
                     slot_views[g][t:t + n] = np.where(pages >= 0, pages * ps + p % ps, -1)
             t += n
         for s in range(n_real, S):          # idle entries
+            if keep and old_rows[s] is not None:
+                for tv in table_views:
+                    tv[s, :] = -1
             tok[t], pos[t] = 0, 0
             cu[s + 1] = t + 1
             kvl[s], qs[s], st[s] = 1, 0, -1
@@ -227,6 +247,7 @@ class BatchBuilder:
         if self._copied is not None:
             self._copied.record()
         self.bytes_last_copy = total * 4
+        self._table_rows = (layout_key, new_rows) if decode_only else None
         if not views:           # a replayed graph reads the arrays where they lie; nobody needs the views
             return None
 
