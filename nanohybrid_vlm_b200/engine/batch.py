@@ -143,6 +143,7 @@ class BatchBuilder:
         decode_only = n_real > 0 and all(len(it.tokens) == 1 and it.want == [0] for it in items)
         keep = decode_only and self._table_rows is not None and self._table_rows[0] == layout_key
         old_rows = self._table_rows[1] if keep else None
+        self._table_rows = None          # a build that fails half-way leaves rows nobody has a record of
         new_rows = [None] * S if decode_only else None
         if not keep:
             for tv in table_views:

@@ -62,6 +62,7 @@ class ModelRunner:
                                                              if b <= config.max_num_seqs]
         self._graphs: dict[int, tuple] = {}
         self._graph_pool = None
+        self.last_logits: torch.Tensor | None = None    # fp32 logits of the last ``run`` (valid until the next one)
 
     def _prepare_decode_weights(self) -> int:
         """Second copies of the matrices that a decode step streams, laid out for the weight-streaming kernel
@@ -127,13 +128,15 @@ class ModelRunner:
             logits = self.model.forward(batch, self.storage)
             out = torch.empty(batch.n_logit_rows, dtype=torch.int32, device=self.device)
             ops.sample(out, logits, batch.temperatures, batch.seeds, batch.sample_positions)
+            self.last_logits = logits
             return out.tolist()
         if bucket not in self._graphs:
             self._capture(bucket)
-        graph, tokens, launches = self._graphs[bucket]
+        graph, tokens, launches, logits = self._graphs[bucket]
         self.builder.build(items, table_width=self.max_pages_per_seq, sampling=sampling, pad_to=bucket, views=False)
         graph.replay()
         library.LAUNCHES += launches     # the kernels that the replay launched
+        self.last_logits = logits[:len(items)]
         return tokens[:len(items)].tolist()
 
     def _bucket(self, items) -> int | None:
@@ -166,7 +169,7 @@ class ModelRunner:
             ops.sample(tokens, logits, batch.temperatures, batch.seeds, batch.sample_positions)
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        self._graphs[bucket] = (graph, tokens, library.LAUNCHES - launches_before)
+        self._graphs[bucket] = (graph, tokens, library.LAUNCHES - launches_before, logits)
 
     @torch.no_grad()
     def sample(self, logits: torch.Tensor, temperatures, seeds, positions) -> list[int]:

@@ -9,7 +9,10 @@ Policy, after nanovllm/engine/scheduler.py (queues :133-134, budget :544-547, po
 * One step = one mixed batch.  Running requests get one token each first ("decode_first");
   what is left of ``max_num_batched_tokens`` goes to the head of ``waiting``, whose prompt is
   cut where the budget ends and goes on from there in the next step.  With
-  "prefill_first" nothing decodes while a request waits.
+  "prefill_first" nothing decodes while a request waits and can be served; when the head of the
+  queue finds no room, the running requests decode instead, finish and make room.  (The
+  reference preempts running requests for the head there, :674-719; with two requests that
+  each fill the pool that never ends, so this engine lets them finish.)
 * A request is admitted only if pages for all its current tokens (and a state slot, if the
   model needs one) are free and fewer than ``max_num_seqs`` requests are live; else the
   queue waits behind it.
@@ -72,26 +75,9 @@ class Scheduler:
         budget = self.max_num_batched_tokens
         scheduled: set[int] = set()
 
-        if not (self.policy == "prefill_first" and self.waiting):
-            for seq in list(self.running):
-                if seq.status != SequenceStatus.RUNNING or budget == 0 or len(plan.seqs) >= self.max_num_seqs:
-                    continue
-                n = len(seq)
-                while not (self.cache.covers(seq.seq_id, n) or self.cache.can_allocate(seq.seq_id, n)):
-                    victim = self._pick_victim(scheduled, exclude=seq)
-                    if victim is None:
-                        victim = seq
-                    self._preempt(victim, plan)
-                    if victim is seq:
-                        break
-                if seq.status != SequenceStatus.RUNNING:
-                    continue
-                self.cache.allocate(seq.seq_id, n)
-                seq.num_scheduled_tokens = 1
-                plan.seqs.append(seq)
-                scheduled.add(seq.seq_id)
-                plan.num_decode_tokens += 1
-                budget -= 1
+        strict_prefill = self.policy == "prefill_first" and bool(self.waiting)
+        if not strict_prefill:
+            budget = self._schedule_decodes(plan, budget, scheduled)
 
         while self.waiting and budget > 0 and len(plan.seqs) < self.max_num_seqs:
             seq = self.waiting[0]
@@ -115,11 +101,39 @@ class Scheduler:
             else:
                 break   # a prompt was cut: the budget (or the portion limit) is used up for this step
 
+        if strict_prefill and not plan.seqs:
+            # the head of the queue found no room (pages, state slot or max_num_seqs): the running requests
+            # go on instead, so that they finish and give back what it waits for
+            budget = self._schedule_decodes(plan, budget, scheduled)
         if not plan.seqs:
             raise RuntimeError("Scheduler cannot make progress: no request fits the free cache pages and budget "
                                f"(waiting {len(self.waiting)}, running {len(self.running)}, free pages "
                                f"{[p.num_free for p in self.cache.pools]})")
         return plan
+
+    def _schedule_decodes(self, plan: SchedulePlan, budget: int, scheduled: set[int]) -> int:
+        """One token for every running request, as far as the budget goes; a request that needs a page when
+        none is free preempts another (or itself).  Returns what is left of the budget."""
+        for seq in list(self.running):
+            if seq.status != SequenceStatus.RUNNING or budget == 0 or len(plan.seqs) >= self.max_num_seqs:
+                continue
+            n = len(seq)
+            while not (self.cache.covers(seq.seq_id, n) or self.cache.can_allocate(seq.seq_id, n)):
+                victim = self._pick_victim(scheduled, exclude=seq)
+                if victim is None:
+                    victim = seq
+                self._preempt(victim, plan)
+                if victim is seq:
+                    break
+            if seq.status != SequenceStatus.RUNNING:
+                continue
+            self.cache.allocate(seq.seq_id, n)
+            seq.num_scheduled_tokens = 1
+            plan.seqs.append(seq)
+            scheduled.add(seq.seq_id)
+            plan.num_decode_tokens += 1
+            budget -= 1
+        return budget
 
     def _pick_victim(self, scheduled: set[int], exclude: Sequence) -> Sequence | None:
         candidates = [s for s in self.running

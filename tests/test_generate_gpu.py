@@ -157,3 +157,18 @@ def test_prefix_reuse_leaves_tokens_unchanged(model_dirs, plain_models):
     off = make_llm(model_dirs["B"], "B", enable_prefix_cache=False)
     assert [o["token_ids"] for o in off.generate(prompts, sp, use_tqdm=False)] == want
     assert off.model_runner.cache.prefix_hits == 0
+
+
+def test_prefill_first_with_a_pool_smaller_than_the_work(model_dirs, plain_models):
+    """"prefill_first" with more requests than places and a pool that holds two of them: the head of the
+    queue waits for room while the running requests decode on; every request gets the plain model's tokens."""
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompts = prompts_for("B", (30, 41, 9, 25, 1, 38), seed=11)
+    want = [plain_models["B"].greedy(p, 9) for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True)
+    # pages of 8 tokens: the longest request ends with 49 tokens = 7 pages; 12 pages hold two requests at most
+    llm = make_llm(model_dirs["B"], "B", num_kvcache_blocks=12, max_num_seqs=3, scheduler_policy="prefill_first",
+                   max_portion=13, enable_prefix_cache=False)
+    assert [o["token_ids"] for o in llm.generate(prompts, sp, use_tqdm=False)] == want
+    llm.model_runner.cache.check()
+    assert all(p.num_free == p.num_pages for p in llm.model_runner.cache.pools)

@@ -131,3 +131,48 @@ def test_a_lone_request_preempts_itself_and_then_nothing_can_progress():
         s.add(seq(64))
     with pytest.raises(RuntimeError, match="cannot make progress"):
         s.schedule()
+
+
+@pytest.mark.parametrize("policy", ["decode_first", "prefill_first"])
+def test_a_pool_smaller_than_the_work_is_worked_off_under_both_policies(policy):
+    """4 pages of 4 tokens, two requests of 9 tokens (3 pages each): the second can be admitted only when
+    the first has finished.  Under "prefill_first" the first decodes on while the second waits for room."""
+    s, cache = make(num_pages=4, page_size=4, policy=policy)
+    a, b = seq(9, max_tokens=3), seq(9, max_tokens=3)
+    s.add(a); s.add(b)
+    _, shape = run_step(s)
+    assert shape == [(a.seq_id, 0, 9)]
+    _, shape = run_step(s)
+    assert shape == [(a.seq_id, 9, 1)]                            # b finds no room, a goes on
+    steps = 2
+    while not s.is_finished():
+        run_step(s)
+        steps += 1
+        assert steps < 20
+    assert a.num_completion_tokens == 3 and b.num_completion_tokens == 3
+    assert cache.pools[0].num_free == 4 and s.num_preemptions == 0
+
+
+@pytest.mark.parametrize("policy", ["decode_first", "prefill_first"])
+def test_more_requests_than_places_and_pages_all_finish(policy):
+    """More requests than max_num_seqs, in a pool that holds two of them at a time, arriving while others
+    run: every one finishes with all its tokens, whatever the policy, and every page comes back."""
+    import random
+    rng = random.Random(3)
+    s, cache = make(num_pages=6, page_size=4, max_num_seqs=2, budget=16, policy=policy, max_model_len=32)
+    todo = [seq(rng.randint(1, 10), max_tokens=rng.randint(1, 6)) for _ in range(9)]
+    all_seqs = list(todo)
+    for q in todo[:3]:
+        s.add(q)
+    todo = todo[3:]
+    steps = 0
+    while todo or not s.is_finished():
+        if todo and (steps % 2 == 0 or s.is_finished()):
+            s.add(todo.pop(0))
+        plan, _ = run_step(s)
+        if policy == "prefill_first" and plan.num_prefill_tokens:
+            assert plan.num_decode_tokens == 0                    # nothing decodes beside a prompt portion
+        steps += 1
+        assert steps < 400
+    assert all(q.is_finished and q.num_completion_tokens == q.max_tokens for q in all_seqs)
+    assert cache.pools[0].num_free == 6
