@@ -6,11 +6,14 @@ device the tensors live on).  It shares no code with the engine: it reads
 tensor names (separate q/k/v and gate/up matrices).
 
 Every function cites the file:line of Bluexvy/NanoHybrid-VLM whose formula it
-restates.  ``tests/golden/make_reference_golden.py`` ran the reference's own
-``Qwen3ForCausalLM`` on the CPU once (its flash-attn call replaced by a masked
-softmax, because that package has no CPU kernel) and stored the logits under
-``tests/golden/``; ``tests/test_plain_vs_reference.py`` compares this file with
-them.  The attention core itself therefore rests on the formula only.
+restates, and the whole is held to the reference's own output twice
+(``tests/test_plain_vs_reference.py``): ``tests/golden/make_reference_golden.py``
+ran the reference's ``Qwen3ForCausalLM`` on the CPU (its flash-attn call
+replaced by a masked softmax, because that package has no CPU kernel), and
+``tests/golden/make_reference_golden_gpu.py`` ran it on a B200 with its real
+attention calls: whole prompts, portions that attend to earlier context in
+the paged cache, single decoded tokens, and its engine generating greedily.
+The logits of both lie under ``tests/golden/``.
 
 ``dtype`` is the storage dtype between ops (the reference's model dtype):
 float32 makes every cast an identity; bfloat16 rounds at the places where the
