@@ -64,7 +64,9 @@ class CacheLayout:
 
 class CacheStorage:
     def __init__(self, layout: CacheLayout, order, page_size: int, num_pages: list[int], num_state_slots: int,
-                 dtype: torch.dtype, device):
+                 dtype: torch.dtype, device, poison: bool = False):
+        """``poison``: the pools start as NaN instead of zeros, so that a kernel that reads a slot which no step
+        has written (beyond a request's tokens, or a page of another request) cannot go unnoticed."""
         self.layout = layout
         self.order = list(order)
         self.page_size = page_size
@@ -73,13 +75,14 @@ class CacheStorage:
         self.states: list[torch.Tensor | None] = []
         for need, g in zip(layout.needs, layout.run_group):
             if isinstance(need, PagedKVNeed):
-                self.pages.append(torch.zeros(num_pages[g], 2, need.num_kv_heads, page_size, need.head_dim,
-                                              dtype=dtype, device=device))
+                self.pages.append(torch.full((num_pages[g], 2, need.num_kv_heads, page_size, need.head_dim),
+                                             float("nan") if poison else 0.0, dtype=dtype, device=device))
                 self.states.append(None)
             elif isinstance(need, FixedStateNeed):
                 sdt = torch.float32 if need.dtype == "float32" else dtype
                 self.pages.append(None)
-                self.states.append(torch.zeros(max(num_state_slots, 1), *need.shape, dtype=sdt, device=device))
+                self.states.append(torch.full((max(num_state_slots, 1), *need.shape), float("nan") if poison else 0.0,
+                                              dtype=sdt, device=device))
             else:
                 self.pages.append(None)
                 self.states.append(None)

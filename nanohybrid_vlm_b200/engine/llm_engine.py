@@ -99,6 +99,8 @@ class LLMEngine:
         self.request_metrics: dict[int, RequestMetrics] = {}
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.last_sampled_ids: list[int] = []   # requests of the last step that chose a token, in the order of the
+                                                # rows of ``model_runner.last_logits``
 
     @staticmethod
     def _load_tokenizer(model_dir: str):
@@ -149,6 +151,7 @@ class LLMEngine:
                 m.first_scheduled_time = t0
         runner = self.model_runner
         tokens = {}
+        self.last_sampled_ids = [s.seq_id for s in sampled]
         if sampled:
             chosen = runner.run(items, [(s.temperature, s.seed, len(s)) for s in sampled])
             self.d2h_bytes += 4 * len(sampled)

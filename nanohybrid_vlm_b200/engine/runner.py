@@ -52,7 +52,8 @@ class ModelRunner:
         config.enable_prefix_cache = possible if config.enable_prefix_cache is None else bool(config.enable_prefix_cache)
         self.cache = CacheManager(self.layout.groups, self.page_size, counts, num_slots,
                                   enable_prefix_cache=config.enable_prefix_cache)
-        self.storage = CacheStorage(self.layout, spec.order, self.page_size, counts, num_slots, self.dtype, self.device)
+        self.storage = CacheStorage(self.layout, spec.order, self.page_size, counts, num_slots, self.dtype, self.device,
+                                    poison=config.poison_cache)
         self.builder = BatchBuilder(self.cache, self.vocab_size, self.device,
                                     max_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,
                                     max_pages_per_seq=self.max_pages_per_seq)

@@ -16,8 +16,12 @@ _libs: dict[int, tuple] = {}
 P, I, F = c_void_p, c_int, c_float
 
 
-def supports(head_dim: int, nq: int, nkv: int) -> bool:
-    return head_dim % 16 == 0 and 16 <= head_dim <= 256 and nq % nkv == 0 and nq // nkv <= 64
+MAX_SEQS = 512      # requests of one step that the kernels plan for (MAX_DECODE_SEQS in the source)
+
+
+def supports(head_dim: int, nq: int, nkv: int, n_seqs: int = 1) -> bool:
+    return (head_dim % 16 == 0 and 16 <= head_dim <= 256 and nq % nkv == 0 and nq // nkv <= 64
+            and n_seqs <= MAX_SEQS)
 
 
 def get(head_dim: int):

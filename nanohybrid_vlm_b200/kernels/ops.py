@@ -130,8 +130,8 @@ def attention_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_t
 def attention(out, q, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int, scale: float, window: int = 0) -> None:
     """Attention of the step's tokens over the cache: picks the kernel for the dtype and sizes.
     bfloat16 with a head size in steps of 16 runs on the tensor cores; everything else (float32, other
-    head sizes, groups of more than 64 heads) on the CUDA cores."""
-    if q.dtype == torch.bfloat16 and attention_mma.supports(head_dim, nq, nkv):
+    head sizes, groups of more than 64 heads, more than 512 requests in the step) on the CUDA cores."""
+    if q.dtype == torch.bfloat16 and attention_mma.supports(head_dim, nq, nkv, batch.n_seqs):
         attention_tensor_core(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs,
                               batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len,
                               nq, nkv, head_dim, scale, window)
@@ -151,7 +151,7 @@ def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int,
     ``qk_norm_rope_store`` does otherwise, in a launch of its own).  Returns False, having done nothing, when
     the step or the shapes do not allow it."""
     if not (FUSE_DECODE_QK and qkv.dtype == torch.bfloat16 and batch.n_prefill_seqs == 0 and batch.n_decode_seqs > 0
-            and attention_mma.supports(head_dim, nq, nkv)):
+            and attention_mma.supports(head_dim, nq, nkv, batch.n_seqs)):
         return False
     launch_fused = attention_mma.get(head_dim)[2]
     vec = head_dim // 32

@@ -67,20 +67,18 @@ def write_random_model(model_dir: str, config: dict, seed: int) -> str:
 
 def materialize_random(model, seed: int) -> dict[str, torch.Tensor]:
     """Fill the model with random weights made on its own device (no file).  Used where writing the
-    checkpoint out would cost more than the run (benchmarks at full size)."""
+    checkpoint out would cost more than the run (benchmarks and replay at full size).
+
+    The rule, so that another program can make the same tensors: every checkpoint tensor is ONE draw of its
+    whole shape in float32 from ``torch.Generator(device).manual_seed(tensor_seed(seed, name))``, then cast.
+    (The device's generator is not the CPU's: a folder written by ``write_random_model`` from the same seed
+    holds other numbers.)"""
     tensors = {}
     for bp in model.param_table():
         dst = torch.empty(bp.decl.shape, dtype=storage_dtype(bp.decl.storage, model.dtype), device=model.device)
         for src in bp.decl.sources:
             gen = torch.Generator(device=model.device).manual_seed(tensor_seed(seed, src.name))
-            rows_left, row = src.rows, src.row
-            # in slabs, so that the fp32 scratch stays small beside a large table
-            slab = max(1, (64 << 20) // max(1, 4 * int(torch.tensor(bp.decl.shape[1:]).prod()) if len(bp.decl.shape) > 1 else 4))
-            while rows_left > 0:
-                n = min(slab, rows_left)
-                dst.narrow(0, row, n).copy_(_draw((n, *bp.decl.shape[1:]), bp.decl.init, gen, model.device))
-                row += n
-                rows_left -= n
+            dst.narrow(0, src.row, src.rows).copy_(_draw((src.rows, *bp.decl.shape[1:]), bp.decl.init, gen, model.device))
         tensors[bp.name] = dst
     model.bind(tensors)
     return tensors

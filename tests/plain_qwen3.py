@@ -137,34 +137,82 @@ def decoder_layer(h, residual, positions, w, i, cfg, cos, sin):
 
 # --------------------------------------------------------------------------- model
 
+def checkpoint_shapes(cfg: dict) -> dict:
+    """Names, shapes and kinds ("matrix" / "norm") of a Qwen3 checkpoint's tensors
+    (nanovllm/models/qwen3.py:42-70,100-109,143-144,169-171,201; q/k/v and gate/up apart, as
+    checkpoints store them, nanovllm/models/qwen3.py:187-193)."""
+    H, nq, nkv, d = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    I, V = cfg["intermediate_size"], cfg["vocab_size"]
+    out = {"model.embed_tokens.weight": ((V, H), "matrix"), "model.norm.weight": ((H,), "norm")}
+    if not cfg["tie_word_embeddings"]:
+        out["lm_head.weight"] = ((V, H), "matrix")
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        out.update({
+            p + "self_attn.q_proj.weight": ((nq * d, H), "matrix"), p + "self_attn.k_proj.weight": ((nkv * d, H), "matrix"),
+            p + "self_attn.v_proj.weight": ((nkv * d, H), "matrix"), p + "self_attn.o_proj.weight": ((H, nq * d), "matrix"),
+            p + "self_attn.q_norm.weight": ((d,), "norm"), p + "self_attn.k_norm.weight": ((d,), "norm"),
+            p + "mlp.gate_proj.weight": ((I, H), "matrix"), p + "mlp.up_proj.weight": ((I, H), "matrix"),
+            p + "mlp.down_proj.weight": ((H, I), "matrix"),
+            p + "input_layernorm.weight": ((H,), "norm"), p + "post_attention_layernorm.weight": ((H,), "norm")})
+    return out
+
+
+def random_weights_on_device(cfg: dict, seed: int, device) -> dict:
+    """The tensors of the engine's random-weights mode WITHOUT a folder, restated from its rule (there is no
+    counterpart in the reference): every checkpoint tensor is one float32 draw of its whole shape on the
+    device from a generator seeded with the first 8 bytes (little-endian, top bit cleared) of
+    sha256("<seed>:<tensor name>"); matrices N(0, 0.02), norm weights 1 + N(0, 0.01)."""
+    import hashlib
+    out = {}
+    for name, (shape, kind) in checkpoint_shapes(cfg).items():
+        digest = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+        gen = torch.Generator(device=device).manual_seed(int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF)
+        t = torch.empty(shape, dtype=torch.float32, device=device)
+        out[name] = t.normal_(0.0, 0.02, generator=gen) if kind == "matrix" else 1.0 + t.normal_(0.0, 0.01, generator=gen)
+    return out
+
+
 class PlainQwen3:
-    def __init__(self, model_dir: str, dtype: torch.dtype = torch.float32):
-        with open(os.path.join(model_dir, "config.json")) as f:
-            cfg = json.load(f)
+    def __init__(self, model_dir: str | None, dtype: torch.dtype = torch.float32, *, cfg: dict | None = None,
+                 weights: dict | None = None):
+        """From a folder (config.json, model.safetensors), or from a config dictionary and a dictionary of
+        tensors under the checkpoint's names (on any device; the model computes where they live)."""
+        if cfg is None:
+            with open(os.path.join(model_dir, "config.json")) as f:
+                cfg = json.load(f)
+        cfg = dict(cfg)
         cfg.setdefault("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"])
         cfg.setdefault("rope_theta", 1000000)
         self.cfg = cfg
         self.dtype = dtype
         self.w = {}
-        with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt", device="cpu") as f:
-            for name in f.keys():
-                self.w[name] = f.get_tensor(name).to(dtype)
+        if weights is not None:
+            self.w = {name: t.to(dtype) for name, t in weights.items()}
+        else:
+            with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt", device="cpu") as f:
+                for name in f.keys():
+                    self.w[name] = f.get_tensor(name).to(dtype)
         if cfg["tie_word_embeddings"]:
             self.w["lm_head.weight"] = self.w["model.embed_tokens.weight"]
+        self.device = self.w["model.norm.weight"].device
         self.cos, self.sin = rope_table(cfg["head_dim"], cfg["max_position_embeddings"], cfg["rope_theta"])
+        self.cos, self.sin = self.cos.to(self.device), self.sin.to(self.device)
 
     @torch.no_grad()
-    def logits(self, token_ids) -> torch.Tensor:
-        """fp32 logits [T, V] at every position of one whole sequence
+    def logits(self, token_ids, rows=None) -> torch.Tensor:
+        """fp32 logits [T, V] at every position of one whole sequence, or at the positions ``rows`` only
         (nanovllm/models/qwen3.py:173-183,205-216; nanovllm/layers/embed_head.py:38,61)."""
         cfg, w = self.cfg, self.w
-        ids = torch.as_tensor(token_ids, dtype=torch.long)
-        positions = torch.arange(len(ids))
+        ids = torch.as_tensor(token_ids, dtype=torch.long, device=self.device)
+        positions = torch.arange(len(ids), device=self.device)
         h = w["model.embed_tokens.weight"][ids]
         residual = None
         for i in range(cfg["num_hidden_layers"]):
             h, residual = decoder_layer(h, residual, positions, w, i, cfg, self.cos, self.sin)
         h, _ = add_rms_norm(h, residual, w["model.norm.weight"], cfg["rms_norm_eps"])
+        if rows is not None:
+            h = h[torch.as_tensor(rows, dtype=torch.long, device=self.device)]
         return linear(h, w["lm_head.weight"]).float()
 
     def greedy(self, prompt, max_tokens: int):

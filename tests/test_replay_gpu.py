@@ -97,3 +97,35 @@ def test_replay_through_the_tcgen05_prompt_kernel(mode, tmp_path):
     out.mkdir()
     got = tt.run_trace(str(model_dir), "bfloat16", MODES[mode](reqs), str(out), vocab=cfg["vocab_size"], page_size=64)
     check(got, ref, reqs, "bfloat16")
+
+
+@pytest.mark.parametrize("page_size", [1, 24, 256])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_with_pages_that_do_not_divide_64(dtype, page_size, model_dirs, references, tmp_path):
+    """Pages of one token, of 24 and of 256 (the reference's own page size): the pool is counted in tokens
+    rounded up to the least common multiple of 64 and the page size, and the logits stay the plain model's."""
+    cfg, _ = TINY["B"]
+    reqs = requests_for("B")
+    got = tt.run_trace(model_dirs["B"], dtype, tt.mixed(reqs), str(tmp_path), vocab=cfg["vocab_size"],
+                       page_size=page_size, max_num_seqs=4)
+    check(got, references["B"], reqs, dtype)
+
+
+def test_replay_from_a_configuration_and_a_seed(tmp_path):
+    """``--config FILE --seed N`` instead of a folder: the weights are made on the device, one draw per checkpoint
+    tensor, and the plain implementation, which makes them by the same rule, gives the same logits."""
+    import json
+    import torch
+    from plain_qwen3 import PlainQwen3, random_weights_on_device
+    cfg, _ = TINY["B"]
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(cfg))
+    plain = PlainQwen3(None, cfg=cfg, weights={k: t.cpu() for k, t in random_weights_on_device(cfg, 77, "cuda").items()})
+    reqs = requests_for("B")
+    ref = {rid: plain.logits(t).numpy() for rid, t in reqs.items()}
+    out = tmp_path / "out"
+    got = tt.run_trace(None, "float32", tt.portions(reqs), str(out), vocab=cfg["vocab_size"], page_size=8,
+                       config_file=str(path), seed=77)
+    check(got, ref, reqs, "float32")
+    assert not torch.equal(plain.w["model.norm.weight"],
+                           PlainQwen3(None, cfg=cfg, weights=random_weights_on_device(cfg, 78, "cpu")).w["model.norm.weight"])

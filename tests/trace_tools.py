@@ -13,8 +13,23 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
 
-def round64(n: int) -> int:
-    return -(-n // 64) * 64
+def round_up(n: int, unit: int = 64) -> int:
+    return -(-n // unit) * unit
+
+
+def thin(steps: list[dict], keep) -> list[dict]:
+    """The same steps with logits wanted only where ``keep(position in the request, request id)`` says so
+    (models with a large vocabulary: every row costs a product with the whole head)."""
+    at: dict = {}
+    out = []
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            base = at.get(e["id"], 0)
+            entries.append(dict(e, want=[w for w in e["want"] if keep(base + w, e["id"])]))
+            at[e["id"]] = base + len(e["tokens"])
+        out.append(dict(st, entries=entries))
+    return out
 
 
 def whole(requests: dict) -> list[dict]:
@@ -86,24 +101,34 @@ def mixed(requests: dict, live: int = 4, first: int = 24, portion: int = 11, see
     return steps
 
 
-def max_live_tokens(steps: list[dict]) -> int:
+def max_live_tokens(steps: list[dict], unit: int = 64) -> int:
+    """The most tokens that live requests hold at any time, each request's count rounded up to ``unit``."""
     held, most = {}, 0
     for st in steps:
         for e in st["entries"]:
             held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
-        most = max(most, sum(round64(n) for n in held.values()))
+        most = max(most, sum(round_up(n, unit) for n in held.values()))
         for rid in st["end"]:
             held.pop(rid, None)
     return most
 
 
-def run_trace(model_dir: str, dtype: str, steps: list[dict], out_dir: str, max_tokens: int | None = None,
-              page_size: int | None = None, vocab: int | None = None, env=None) -> dict:
-    """Run bin/trace_run; returns {request: {position: logits row}}."""
-    cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-           "--max-tokens", str(max_tokens or max_live_tokens(steps))]
+def run_trace(model_dir: str | None, dtype: str, steps: list[dict], out_dir: str, max_tokens: int | None = None,
+              page_size: int | None = None, vocab: int | None = None, env=None, poison: bool = True,
+              config_file: str | None = None, seed: int | None = None, max_num_seqs: int | None = None) -> dict:
+    """Run bin/trace_run (on a folder, or on ``config_file`` and ``seed``); returns {request: {position: logits row}}.
+    The cache pools start as NaN unless ``poison`` is False."""
+    import math
+    unit = math.lcm(64, page_size) if page_size else 64
+    cmd = [sys.executable, TRACE_RUN, "--dtype", dtype, "--out", out_dir,
+           "--max-tokens", str(max_tokens or max_live_tokens(steps, unit))]
+    cmd += ["--model", model_dir] if config_file is None else ["--config", config_file, "--seed", str(seed)]
     if page_size:
         cmd += ["--page-size", str(page_size)]
+    if max_num_seqs:
+        cmd += ["--max-num-seqs", str(max_num_seqs)]
+    if poison:
+        cmd += ["--poison"]
     text = "".join(json.dumps(s) + "\n" for s in steps)
     r = subprocess.run(cmd, input=text, capture_output=True, text=True, env=env)
     assert r.returncode == 0, f"trace_run failed ({r.returncode}):\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
