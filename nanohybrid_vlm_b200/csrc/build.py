@@ -142,14 +142,16 @@ def ensure_built(verbose: bool = True) -> str:
     return os.path.join(bdir, LIB_NAME)
 
 
-def ensure_variant(source: str, defines: dict, verbose: bool = True) -> str:
+def ensure_variant(source: str, defines: dict, verbose: bool = True, folder: str = "variants") -> str:
     """Compile one file of ``csrc/variants/`` with the given -D values into a library of its own
-    (for kernels whose sizes are compile-time constants: a model compiles only what it needs)."""
-    src = os.path.join(CSRC, "variants", source)
+    (for kernels whose sizes are compile-time constants: a model compiles only what it needs).
+    ``folder=""`` takes a file of ``csrc/`` itself (tests build a kernel with other constants that way)."""
+    src = os.path.join(CSRC, folder, source)
     tag = "_".join(f"{k.lower()}{v}" for k, v in sorted(defines.items()))
     name = f"libnhv_{os.path.splitext(source)[0]}_{tag}.so"
     h = hashlib.sha256()
-    for path in (src, os.path.join(CSRC, "nhv_common.cuh")):
+    headers = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+    for path in (src, *headers):
         with open(path, "rb") as f:
             h.update(f.read())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode() + repr(sorted(defines.items())).encode())

@@ -22,10 +22,16 @@
 // Modes: 0: y bf16.  1: y fp32, rounded through bf16 as nanovllm/layers/embed_head.py:61 with
 // nanovllm/layers/sampler.py:12 gives logits.  2: y = silu(gate) * up (nanovllm/layers/activation.py:9-11), both
 // products rounded to bf16 first.  W is [out, in] (nanovllm/layers/linear.py:40,66).
-#include <cuda.h>
-#include <cudaTypedefs.h>
+#include "nhv_async.cuh"
 
-#include "nhv_common.cuh"
+// Test builds only (tests compile this file into a library of its own with a short NHV_WAIT_LIMIT): the producer
+// leaves the copies of ring unit NHV_TEST_DROP_UNIT unsent, so that the consumers' wait for it runs out and the
+// way out of a run-out wait (error word, delay, ordinary exit) is exercised without a fault or a hang.
+#ifdef NHV_TEST_DROP_UNIT
+#define NHV_UNIT_IS_SENT(i) ((i) != (NHV_TEST_DROP_UNIT))
+#else
+#define NHV_UNIT_IS_SENT(i) true
+#endif
 
 namespace {
 
@@ -40,44 +46,7 @@ constexpr int MAX_NB = 8;                // at most 8 boxes of 64 columns per st
 constexpr int W_STAGE_BYTES = 32 * 1024; // rows * nb * 128 bytes never exceeds this
 constexpr int X_BOX_BYTES = X_ROWS * 128;
 constexpr int STAGE_BYTES = W_STAGE_BYTES + MAX_NB * X_BOX_BYTES;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-__device__ int g_error = 0;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait: false (and the error word set) if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  atomicExch(&g_error, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-               ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-// A linear copy: both addresses 16-byte aligned, the size a multiple of 16 bytes.
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
@@ -88,11 +57,6 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
-// After a wait ran out: give copies that may still be in flight time to land before the block leaves.
-__device__ __forceinline__ void give_up_delay() {
-  for (int i = 0; i < 2000; ++i) __nanosleep(200);
-}
-
 struct alignas(64) Params {
   CUtensorMap x_map;     // x [M, K], box 64 columns x 8 rows
   const unsigned char* slabs;
@@ -152,16 +116,20 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_slab_kernel(const __grid_cons
       };
       // Fill the ring with weights while the kernel before this one may still be running, then wait for it.
       const int pre = min(STAGES, units);
-      for (int i = 0; i < pre; ++i) issue_w(i);
+      for (int i = 0; i < pre; ++i)
+        if (NHV_UNIT_IS_SENT(i)) issue_w(i);
       pdl_wait();
-      for (int i = 0; i < pre; ++i) issue_x(i);
+      for (int i = 0; i < pre; ++i)
+        if (NHV_UNIT_IS_SENT(i)) issue_x(i);
       bool ok = true;
       for (int i = STAGES; i < units; ++i) {
         const int s = i % STAGES;
         ok = mbar_wait(&empty[s], (uint32_t)((i / STAGES) - 1) & 1, 1);
         if (!ok) break;
-        issue_w(i);
-        issue_x(i);
+        if (NHV_UNIT_IS_SENT(i)) {
+          issue_w(i);
+          issue_x(i);
+        }
       }
       if (!ok) give_up_delay();
     } else {
@@ -247,33 +215,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_slab_kernel(const __grid_cons
   }
 }
 
-PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
-
 bool make_x_map(CUtensorMap* map, const void* base, int rows, int cols, int row_stride_elems) {
-  if (!g_encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
-    g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
-  }
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
-  const cuuint32_t box[2] = {64, (cuuint32_t)X_ROWS};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return nhv_make_map_bf16(map, base, rows, cols, row_stride_elems, 64, X_ROWS);
 }
 
 }  // namespace
 
 // Reads and clears the error word (0: no bounded wait ever ran out).  Synchronises the device.
-NHV_API int nhv_gemm_slab_error() {
-  int v = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) cudaMemcpyToSymbol(g_error, &zero, sizeof(int));
-  return v;
-}
+NHV_API int nhv_gemm_slab_error() { return nhv_wait_error_take(); }
+// The device address of the error word, for kernels that report it with the step's result.
+NHV_API void* nhv_gemm_slab_error_word() { return nhv_wait_error_address(); }
 
 // The geometry of the copy for a matrix with N result columns (mode 2: N = half the rows of W) and K columns on a
 // device with `sms` SMs: blocks, result columns per block, boxes per stage, stages over K, bytes per block.

@@ -26,13 +26,12 @@
 //
 // Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host
 // reads with nhv_gemm_stream_k_error().
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
-#include "nhv_common.cuh"
+#include "nhv_async.cuh"
+#include "nhv_no_alloc.h"
 
 namespace {
 
@@ -41,52 +40,6 @@ constexpr int ROWS = 64;                 // weight rows per tile (4 MMA row tile
 constexpr int MT = ROWS / 16;
 constexpr int CONSUMER_WARPS = 4;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
-
-__device__ int g_error = 0;
-#ifdef NHV_STREAM_K_TIMING
-__device__ unsigned long long g_times[8][256][6];   // [launch % 8][block][event]
-__device__ int g_launch_no = 0;
-__device__ __forceinline__ unsigned long long now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define STAMP(slot, ev) do { if (lane == 0) g_times[(slot) & 7][blockIdx.x & 255][ev] = now_ns(); } while (0)
-#else
-#define STAMP(slot, ev) do {} while (0)
-#endif
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait: false (and the error word set) if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  atomicExch(&g_error, code);
-  return false;
-}
-// One box of the tensor described by `map`, starting at column x (a multiple of 8) and row y.
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-               ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
@@ -106,11 +59,6 @@ __device__ __forceinline__ int arrive_acq_rel(int* counter) {
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { pdl_wait(); }
 __device__ __forceinline__ void launch_dependents() { pdl_launch_dependents(); }
-
-// After a wait ran out: give copies that may still be in flight time to land before the block leaves.
-__device__ __forceinline__ void give_up_delay() {
-  for (int i = 0; i < 2000; ++i) __nanosleep(200);
-}
 
 #ifndef NHV_STREAM_K_BK
 #define NHV_STREAM_K_BK 256
@@ -158,13 +106,6 @@ __global__ void __launch_bounds__(THREADS, NHV_STREAM_K_BK <= 128 ? 2 : 1) gemm_
   const long long total = (long long)tiles * kb;
   const long long u0 = unit_begin(c, total, G), u1 = unit_begin(c + 1, total, G);
 
-#ifdef NHV_STREAM_K_TIMING
-  const int t_slot = p.lda >> 20;      // experiments pass the launch number in the high bits of lda
-#else
-  const int t_slot = 0;
-#endif
-  (void)t_slot;
-  if (warp == 0) STAMP(t_slot, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -206,9 +147,7 @@ __global__ void __launch_bounds__(THREADS, NHV_STREAM_K_BK <= 128 ? 2 : 1) gemm_
       // Fill the ring with weights while the kernel before this one may still be running, then wait for it.
       const int pre = (int)min((long long)STAGES, n_units);
       for (int i = 0; i < pre; ++i) issue_w(i);
-      STAMP(t_slot, 1);
       grid_dependency_wait();
-      STAMP(t_slot, 2);
       for (int i = 0; i < pre; ++i) issue_x(i);
       bool ok = true;
       for (long long i = STAGES; i < n_units; ++i) {
@@ -303,8 +242,6 @@ __global__ void __launch_bounds__(THREADS, NHV_STREAM_K_BK <= 128 ? 2 : 1) gemm_
       const int tile = (int)(u / kb), k = (int)(u - (long long)tile * kb);
       ok = mbar_wait(&full[s], (uint32_t)(i / STAGES) & 1, 2);
       if (!ok) { give_up_delay(); break; }
-      if (warp == 0 && i == 0) STAMP(t_slot, 3);
-      if (warp == 0 && u == u1 - 1) STAMP(t_slot, 4);
       // this warp's box of the stage; inside a box row r holds its 16-byte chunk c at chunk (c ^ (r & 7))
       const int my_box = warp * KSTEPS * 16 / BOX_COLS;
       const unsigned char* ws = ring + (size_t)s * STAGE_BYTES + my_box * W_BOX_BYTES;
@@ -385,7 +322,6 @@ __global__ void __launch_bounds__(THREADS, NHV_STREAM_K_BK <= 128 ? 2 : 1) gemm_
       consumer_sync();
       if (s_flag == tile_pieces(deferred_tile) - 1) finish_shared_tile(deferred_tile);
     }
-    if (warp == 0) STAMP(t_slot, 5);
   }
 }
 
@@ -394,11 +330,14 @@ int launch(const Params& p, int grid, cudaStream_t stream) {
   constexpr int X_ROWS = NT * 8;
   constexpr size_t smem = 1024 + (size_t)STAGES * BOXES * (ROWS + X_ROWS) * 128 + (size_t)CONSUMER_WARPS * ROWS * X_ROWS * 4 +
                           2 * STAGES * 8;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the attribute belongs to the device that is current: set once for each
+  static std::atomic<bool> attr_set[64];
+  int dev = 0;
+  NHV_CUDA(cudaGetDevice(&dev), "gemm_stream_k");
+  if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
     NHV_CUDA(cudaFuncSetAttribute(gemm_stream_k_kernel<NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)smem), "gemm_stream_k");
-    attr_set = true;
+    if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -415,22 +354,8 @@ int launch(const Params& p, int grid, cudaStream_t stream) {
 }
 
 // ---------------------------------------------------------------- tensor maps (host)
-PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
-
 bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int row_stride_elems, int box_rows) {
-  if (!g_encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
-    g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
-  }
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BOX_COLS, (cuuint32_t)box_rows};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return nhv_make_map_bf16(map, base, rows, cols, row_stride_elems, BOX_COLS, box_rows);
 }
 
 struct MapKey {
@@ -457,21 +382,14 @@ NHV_API int nhv_gemm_stream_k_scratch(int grid, int max_tiles, size_t* partial_f
 }
 
 // Reads and clears the error word (0: no bounded wait ever ran out).  Synchronises the device.
-NHV_API int nhv_gemm_stream_k_error() {
-  int v = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) cudaMemcpyToSymbol(g_error, &zero, sizeof(int));
-  return v;
-}
+NHV_API int nhv_gemm_stream_k_error() { return nhv_wait_error_take(); }
+// The device address of the error word, for kernels that report it with the step's result.
+NHV_API void* nhv_gemm_stream_k_error_word() { return nhv_wait_error_address(); }
 
 NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int N, int K, int lda, int ldc, int mode,
                               int up_row_offset, float* scratch, int* counters, int counters_len, int grid,
                               cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-#ifdef NHV_STREAM_K_TIMING
-  const int timing_slot = lda >> 20;
-  lda &= (1 << 20) - 1;
-#endif
   NHV_REQUIRE(M > 0 && M <= 16, "gemm_stream_k: takes 1 to 16 tokens, got %d", M);
   NHV_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && lda >= K && ldc >= N,
               "gemm_stream_k: K and the row stride of x must be multiples of 8 (N=%d K=%d lda=%d)", N, K, lda);
@@ -483,9 +401,6 @@ NHV_API int nhv_gemm_stream_k(void* y, const void* x, const void* W, int M, int 
   Params p;
   p.y = y; p.x = (const bf16*)x; p.W = (const bf16*)W; p.scratch = scratch; p.counters = counters;
   p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset;
-#ifdef NHV_STREAM_K_TIMING
-  p.lda = lda | (timing_slot << 20);
-#endif
   const int w_rows = mode == 2 ? up_row_offset + N : N, w_box = mode == 2 ? ROWS / 2 : ROWS;
   {
     std::lock_guard<std::mutex> lock(g_maps_mutex);
@@ -521,7 +436,9 @@ constexpr int STATIC_MAX_DEVICES = 64;
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_PARTIAL_BYTES + STATIC_COUNTER_BYTES];
 
 struct StaticScratch {
-  unsigned char* base = nullptr;   // device address of g_static_scratch on this device
+  // device address of g_static_scratch on this device; stored last (release) by the thread that sets the device
+  // up, so that a thread that sees it (acquire) also sees `sms`
+  std::atomic<unsigned char*> base{nullptr};
   int sms = 0;
 };
 StaticScratch g_static[STATIC_MAX_DEVICES];
@@ -546,11 +463,13 @@ NHV_API int nhv_gemm_stream_k_no_alloc(void* y, const void* x, const void* W, in
   NHV_REQUIRE(dev >= 0 && dev < STATIC_MAX_DEVICES, "gemm_stream_k_no_alloc: device %d is beyond the %d this library tracks", dev,
               STATIC_MAX_DEVICES);
   StaticScratch* st = &g_static[dev];
-  if (st->base == nullptr) {
+  unsigned char* base = st->base.load(std::memory_order_acquire);
+  if (base == nullptr) {
     // Set-up, once per device, with that device current.  In host code the array's name only stands for the
     // symbol; the address a kernel can use comes from cudaGetSymbolAddress.
     std::lock_guard<std::mutex> lock(g_static_mutex);
-    if (st->base == nullptr) {
+    base = st->base.load(std::memory_order_acquire);
+    if (base == nullptr) {
       unsigned char* ptr = nullptr;
       NHV_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch), "gemm_stream_k_no_alloc: address of the built-in scratch");
       NHV_REQUIRE(ptr != nullptr, "gemm_stream_k_no_alloc: the built-in scratch has no device address");
@@ -559,14 +478,15 @@ NHV_API int nhv_gemm_stream_k_no_alloc(void* y, const void* x, const void* W, in
       // the counters must start at zero (the kernel returns them to zero after every call that completes)
       NHV_CUDA(cudaMemsetAsync(ptr + STATIC_PARTIAL_BYTES, 0, STATIC_COUNTER_BYTES, stream), "gemm_stream_k_no_alloc");
       st->sms = sms;
-      st->base = ptr;
+      st->base.store(ptr, std::memory_order_release);
+      base = ptr;
     }
   }
   int grid = st->sms < STATIC_MAX_GRID ? st->sms : STATIC_MAX_GRID;
   Params p;
   p.y = y; p.x = (const bf16*)x; p.W = (const bf16*)W;
-  p.scratch = reinterpret_cast<float*>(st->base);
-  p.counters = reinterpret_cast<int*>(st->base + STATIC_PARTIAL_BYTES);
+  p.scratch = reinterpret_cast<float*>(base);
+  p.counters = reinterpret_cast<int*>(base + STATIC_PARTIAL_BYTES);
   p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.mode = mode; p.up_row_offset = up_row_offset;
   const int w_rows = mode == 2 ? up_row_offset + N : N, w_box = mode == 2 ? ROWS / 2 : ROWS;
   // both tensor maps are encoded on the stack: no cache, nothing allocated on the host either
@@ -578,9 +498,3 @@ NHV_API int nhv_gemm_stream_k_no_alloc(void* y, const void* x, const void* W, in
   return launch<2, NHV_STREAM_K_STAGES>(p, grid, stream);
 }
 
-#ifdef NHV_STREAM_K_TIMING
-// Experiments only: the time stamps [8 launches][256 blocks][6 events] in nanoseconds of the global timer.
-NHV_API int nhv_gemm_stream_k_times(unsigned long long* host) {
-  return cudaMemcpyFromSymbol(host, g_times, sizeof(g_times)) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -25,13 +25,11 @@
 // (nhv_gemm_tcgen05_error) and the block leaves through the common exit, which frees its tensor
 // memory.  Modes as in gemm_stream_k.cu: 0 bf16, 1 fp32 through bf16, 2 silu(gate) * up (a tile is
 // 64 gate rows and the same 64 rows of up).  W is [out, in] (nanovllm/layers/linear.py:40,66).
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
 #include <mutex>
 #include <unordered_map>
 
-#include "nhv_common.cuh"
+#define NHV_WAIT_LIMIT (1u << 22)
+#include "nhv_async.cuh"
 
 namespace {
 
@@ -41,41 +39,6 @@ constexpr int BK = 64;                 // columns per stage = one 128-byte swizz
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;           // producer warp, MMA warp, four epilogue warps
 constexpr int EPI_THREADS = 128;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
-
-__device__ int g_error = 0;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait: false (and the error word set) if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  atomicExch(&g_error, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-               ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-
-// ---- tensor memory and tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot_in_smem)), "r"(ncols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -132,9 +95,6 @@ __device__ __forceinline__ uint32_t instr_desc(int m, int n) {
 }
 
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(EPI_THREADS) : "memory"); }
-__device__ __forceinline__ void give_up_delay() {
-  for (int i = 0; i < 2000; ++i) __nanosleep(200);
-}
 
 struct alignas(64) Params {
   CUtensorMap w_map;    // W [N, K], box 64 columns x 128 rows (mode 2: x 64 rows)
@@ -399,22 +359,8 @@ int launch(const Params& p, int grid, cudaStream_t stream) {
   return 0;
 }
 
-PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
-
 bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int row_stride_elems, int box_rows) {
-  if (!g_encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
-    g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
-  }
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return nhv_make_map_bf16(map, base, rows, cols, row_stride_elems, BK, box_rows);
 }
 
 struct MapKey {
@@ -433,12 +379,9 @@ std::mutex g_maps_mutex;
 }  // namespace
 
 // Reads and clears the error word (0: no bounded wait ever ran out).  Synchronises the device.
-NHV_API int nhv_gemm_tcgen05_error() {
-  int v = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) cudaMemcpyToSymbol(g_error, &zero, sizeof(int));
-  return v;
-}
+NHV_API int nhv_gemm_tcgen05_error() { return nhv_wait_error_take(); }
+// The device address of the error word, for kernels that report it with the step's result.
+NHV_API void* nhv_gemm_tcgen05_error_word() { return nhv_wait_error_address(); }
 
 // Tokens per MMA column tile for a batch of M tokens (the scratch is [grid][2][128][this] floats).
 NHV_API int nhv_gemm_tcgen05_token_tile(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }

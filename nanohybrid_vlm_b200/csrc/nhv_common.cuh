@@ -13,8 +13,22 @@
 
 enum NhvDtype { NHV_F32 = 0, NHV_BF16 = 1 };
 
+#ifdef NHV_OWN_ERROR_TEXT
+// A file compiled into a library of its own (tests do that) keeps the text of its last error itself and exports
+// nhv_last_error() for it.
+#include <stdarg.h>
+static char nhv_own_error_text[512];
+static void nhv_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(nhv_own_error_text, sizeof(nhv_own_error_text), fmt, ap);
+  va_end(ap);
+}
+NHV_API const char* nhv_last_error() { return nhv_own_error_text; }
+#else
 // Defined in elementwise.cu.
 void nhv_set_error(const char* fmt, ...);
+#endif
 
 #define NHV_REQUIRE(cond, ...)                                  \
   do {                                                          \

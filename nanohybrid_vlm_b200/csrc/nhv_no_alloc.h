@@ -27,6 +27,8 @@
 //    clearing (every block writes its slot before any block reads it); the counters must be zero when a call
 //    starts, and every call that runs to completion leaves them zero.  Two calls that overlap on the GPU
 //    (different streams, or two host threads) race on the array and give wrong results: serialise them.
+//  * Host threads: the per-device set-up is guarded, so first calls from several threads are safe; the calls
+//    themselves are safe from several threads only in the sense above (their GPU work must not overlap).
 //  * Returns 0 on success, 1 for a refused argument, 2 for a CUDA error.
 #pragma once
 #include <cuda_runtime.h>
@@ -35,7 +37,7 @@
 extern "C" {
 #endif
 
-int nhv_gemm_stream_k_no_alloc(void* y, const void* x, const void* W, int M, int N, int K, int lda, int ldc, int mode,
+__attribute__((visibility("default"))) int nhv_gemm_stream_k_no_alloc(void* y, const void* x, const void* W, int M, int N, int K, int lda, int ldc, int mode,
                                int up_row_offset, cudaStream_t stream);
 
 #ifdef __cplusplus

@@ -34,14 +34,29 @@ __device__ __forceinline__ unsigned long long score_key(float s, int i) {
 // A row is cut into gridDim.y pieces, one block each; the blocks meet at the row's slot of `best` (atomic
 // maximum of the keys) and count their arrival; the block that arrives last writes the row's token and
 // returns slot and counter to zero for the next launch.  No block waits for another.
+//
+// The sampler is the last kernel of a step and its result is what the host reads, so it also carries the step's
+// health: `error_words` holds device addresses of the error words of kernels with bounded waits (null entries
+// are skipped); bit i of *status is set if word i is not zero.  Every kernel of the step has completed when this
+// one reads them (it waits for its predecessor before reading anything).
 __global__ void __launch_bounds__(256) sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
                                                      int ld, const float* __restrict__ temperatures,
                                                      const unsigned long long* __restrict__ seeds,
                                                      const int* __restrict__ positions, int vocab,
-                                                     unsigned long long* __restrict__ best, int* __restrict__ arrived) {
+                                                     unsigned long long* __restrict__ best, int* __restrict__ arrived,
+                                                     const int* const* __restrict__ error_words, int n_error_words,
+                                                     int* __restrict__ status) {
   __shared__ unsigned long long warp_best[8];
   pdl_prologue();
   const int row = blockIdx.x;
+  if (status != nullptr && row == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+    int bits = 0;
+    for (int i = 0; i < n_error_words && i < 31; ++i) {
+      const int* word = error_words[i];
+      if (word != nullptr && *reinterpret_cast<const volatile int*>(word) != 0) bits |= 1 << i;
+    }
+    *status = bits;
+  }
   const float* lg = logits + (size_t)row * ld;
   const float temp = temperatures[row];
   const unsigned long long seed = seeds[row];
@@ -98,10 +113,13 @@ __global__ void __launch_bounds__(256) sample_kernel(int* __restrict__ out, cons
   }
 }
 
-// best [n_rows] 64-bit words and arrived [n_rows] ints, all zero (the kernel leaves them zero).
+// best [n_rows] 64-bit words and arrived [n_rows] ints, all zero (the kernel leaves them zero).  error_words:
+// device array of n_error_words device addresses (or null entries), status: one int on the device; both may be
+// null, then no health is reported.
 NHV_API int nhv_sample(int* out, const float* logits, int ld, const float* temperatures,
                        const unsigned long long* seeds, const int* positions, int n_rows, int vocab,
-                       unsigned long long* best, int* arrived, cudaStream_t stream) {
+                       unsigned long long* best, int* arrived, const int* const* error_words, int n_error_words,
+                       int* status, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NHV_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab && best && arrived, "sample: bad arguments");
   // pieces of about 8,192 scores, but no more blocks than a few per SM
@@ -109,7 +127,7 @@ NHV_API int nhv_sample(int* out, const float* logits, int ld, const float* tempe
   const int room = 148 * 4 / n_rows;
   if (pieces > room) pieces = room < 1 ? 1 : room;
   nhv_launch(sample_kernel, dim3(n_rows, pieces), 256, 0, stream, out, logits, ld, temperatures, seeds, positions, vocab,
-             best, arrived);
+             best, arrived, error_words, error_words ? n_error_words : 0, error_words ? status : (int*)nullptr);
   NHV_CHECK_LAUNCH("sample");
   return 0;
 }

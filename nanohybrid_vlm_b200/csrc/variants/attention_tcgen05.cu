@@ -32,7 +32,8 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "nhv_common.cuh"
+#define NHV_WAIT_LIMIT (1u << 22)
+#include "nhv_async.cuh"
 
 #ifndef NHV_ATTN_D
 #error "compile with -DNHV_ATTN_D=<head size>"
@@ -59,42 +60,11 @@ constexpr int SMEM_NEED = 1024 + Q_BYTES + 2 * STAGES * T_BYTES;    // barriers 
 constexpr int SMEM_BYTES = SMEM_NEED < 80 * 1024 ? 80 * 1024 : SMEM_NEED;
 constexpr uint32_t TMEM_COLS = (2 * BN + D) <= 256 ? 256 : 512;
 constexpr uint32_t S_COL = 0, O_COL = 2 * BN;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr float RESCALE_STEP = 8.0f;         // log2 units
 constexpr float LOG2E = 1.4426950408889634f;
 
-__device__ int g_error = 0;
 char g_err[256] = "";
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait: false (and the error word set) if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  atomicExch(&g_error, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-               ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
 // ---- tensor memory and tcgen05
@@ -245,7 +215,7 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
     tile -= nt;
   }
   const bool active = seq >= 0 && (raw & 127u) == 0;
-  if (seq >= 0 && !active && threadIdx.x == 0) atomicExch(&g_error, 9);
+  if (seq >= 0 && !active && threadIdx.x == 0) wait_error_set(9);
   int n_new = 0, total = 0, t0 = 0, tq_n = 0, pos0 = 0, q_row0 = 0;
   if (active) {
     q_row0 = p.cu_q[seq];
@@ -490,22 +460,8 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
   }
 }
 
-PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
-
 bool make_map(CUtensorMap* map, const void* base, long long rows) {
-  if (!g_encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
-    g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
-  }
-  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-  const cuuint32_t box[2] = {64, (cuuint32_t)BN};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return nhv_make_map_bf16(map, base, rows, D, D, 64, BN);
 }
 
 struct MapKey {
@@ -542,12 +498,10 @@ bool set_attributes() {
 
 NHV_API const char* NHV_FN(nhv_attn_tcgen05_last_error_d)() { return g_err; }
 
-// The error word of the kernels' bounded waits (0 = none); reading it synchronizes with the device.
-NHV_API int NHV_FN(nhv_attn_tcgen05_error_d)() {
-  int e = -1;
-  if (cudaMemcpyFromSymbol(&e, g_error, sizeof(int)) != cudaSuccess) return -1;
-  return e;
-}
+// Reads and clears the error word of the kernel's bounded waits (0: none ran out).  Synchronises the device.
+NHV_API int NHV_FN(nhv_attn_tcgen05_error_d)() { return nhv_wait_error_take(); }
+// The device address of the error word, for kernels that report it with the step's result.
+NHV_API void* NHV_FN(nhv_attn_tcgen05_error_word_d)() { return nhv_wait_error_address(); }
 
 // Attention of the step's prompt portions (requests with more than one new token); requests with one new token
 // are left alone.  The page size must be a multiple of 64.

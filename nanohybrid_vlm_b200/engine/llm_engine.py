@@ -154,7 +154,7 @@ class LLMEngine:
         self.last_sampled_ids = [s.seq_id for s in sampled]
         if sampled:
             chosen = runner.run(items, [(s.temperature, s.seed, len(s)) for s in sampled])
-            self.d2h_bytes += 4 * len(sampled)
+            self.d2h_bytes += 4 * (len(sampled) + 1)        # the tokens and the step's health word
             tokens = {s.seq_id: t for s, t in zip(sampled, chosen)}
         else:
             runner.step(items)

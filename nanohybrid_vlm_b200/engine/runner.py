@@ -127,10 +127,10 @@ class ModelRunner:
         if bucket is None:
             batch = self.builder.build(items, sampling=sampling)
             logits = self.model.forward(batch, self.storage)
-            out = torch.empty(batch.n_logit_rows, dtype=torch.int32, device=self.device)
+            out = torch.empty(batch.n_logit_rows + 1, dtype=torch.int32, device=self.device)   # tokens, health word
             ops.sample(out, logits, batch.temperatures, batch.seeds, batch.sample_positions)
             self.last_logits = logits
-            return out.tolist()
+            return self._checked(out.tolist())
         if bucket not in self._graphs:
             self._capture(bucket)
         graph, tokens, launches, logits = self._graphs[bucket]
@@ -138,7 +138,21 @@ class ModelRunner:
         graph.replay()
         library.LAUNCHES += launches     # the kernels that the replay launched
         self.last_logits = logits[:len(items)]
-        return tokens[:len(items)].tolist()
+        host = tokens.tolist()           # one read: the bucket's tokens and the health word behind them
+        return self._checked(host[:len(items)] + host[-1:])
+
+    @staticmethod
+    def _checked(tokens_and_health: list[int]) -> list[int]:
+        """The step's tokens, if no bounded wait of a kernel ran out during the step (the health word that the
+        sampler wrote behind the tokens is zero); else ``KernelError`` naming the kernel."""
+        if tokens_and_health[-1] != 0:
+            ops.raise_wait_errors()
+        return tokens_and_health[:-1]
+
+    def check_kernels(self) -> None:
+        """For callers of ``step`` (logits, no sampler): raise ``KernelError`` if a bounded wait of a kernel ran
+        out since the last check.  Synchronises the device."""
+        ops.raise_wait_errors()
 
     def _bucket(self, items) -> int | None:
         if not self.graph_buckets or len(items) > self.graph_buckets[-1]:
@@ -154,7 +168,7 @@ class ModelRunner:
         def one_step():
             batch = self.builder.build([], table_width=self.max_pages_per_seq, sampling=[], pad_to=bucket)
             logits = self.model.forward(batch, self.storage)
-            out = torch.empty(bucket, dtype=torch.int32, device=self.device)
+            out = torch.empty(bucket + 1, dtype=torch.int32, device=self.device)
             ops.sample(out, logits, batch.temperatures, batch.seeds, batch.sample_positions)
             return out
 
@@ -166,7 +180,7 @@ class ModelRunner:
         launches_before = library.LAUNCHES
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = self.model.forward(batch, self.storage)
-            tokens = torch.empty(bucket, dtype=torch.int32, device=self.device)
+            tokens = torch.empty(bucket + 1, dtype=torch.int32, device=self.device)     # tokens, health word
             ops.sample(tokens, logits, batch.temperatures, batch.seeds, batch.sample_positions)
         if self._graph_pool is None:
             self._graph_pool = graph.pool()

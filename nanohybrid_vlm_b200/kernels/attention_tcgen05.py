@@ -23,7 +23,8 @@ def supports(head_dim: int, nq: int, nkv: int, page_size: int) -> bool:
 
 
 def get(head_dim: int):
-    """(launch function, error-word reader) for this head size."""
+    """(launch function, function that reads and clears the error word) for this head size.  The error word is
+    also registered with the step's health word (``ops.register_wait_error_source``)."""
     if head_dim not in _libs:
         from ..csrc.build import ensure_variant
         lib = ctypes.CDLL(ensure_variant("attention_tcgen05.cu", {"NHV_ATTN_D": head_dim}))
@@ -34,6 +35,10 @@ def get(head_dim: int):
         err.restype = ctypes.c_char_p
         word = getattr(lib, f"nhv_attn_tcgen05_error_d{head_dim}")
         word.restype = c_int
+        address = getattr(lib, f"nhv_attn_tcgen05_error_word_d{head_dim}")
+        address.restype, address.argtypes = c_void_p, []
+        from . import ops
+        ops.register_wait_error_source(f"attention_tcgen05 (head size {head_dim})", address, word)
 
         def launch(*args, _fn=fn, _err=err):
             if _fn(*args) != 0:

@@ -25,7 +25,7 @@ _SIGNATURES = {
     "nhv_qk_norm_rope_store": [I, P, I, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P],
     "nhv_attention_simt": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, F, P],
     "nhv_gemm_nt_simt": [I, P, P, P, I, I, I, I, I, I, I, P],
-    "nhv_sample": [P, P, I, P, P, P, I, I, P, P, P],
+    "nhv_sample": [P, P, I, P, P, P, I, I, P, P, P, I, P, P],
     "nhv_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, P],
     "nhv_gemm_stream_k": [P, P, P, I, I, I, I, I, I, I, P, P, I, I, P],
     "nhv_gemm_slab": [P, P, P, I, I, I, I, I, I, I, P],

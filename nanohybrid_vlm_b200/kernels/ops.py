@@ -479,9 +479,77 @@ def linear_simt(out, x, weight) -> None:
          N, int(out.dtype == torch.float32 and x.dtype != torch.float32), stream_ptr())
 
 
+# ---------------------------------------------------------------- bounded waits that ran out
+# Kernels that wait on mbarriers bound their waits; one that runs out sets its file's error word and the kernel
+# leaves with whatever it has, so the step's results are not valid.  The words reach the host with the step's
+# tokens: the sampler folds them into one more int behind the tokens (``sample`` below), and callers that read
+# logits instead ask ``take_wait_errors`` once per step.
+ERROR_WORD_SLOTS = 16
+_wait_error_sources: list = []          # (name, function giving the word's device address, function that reads and clears it)
+_error_word_arrays: dict = {}           # device -> (int64 tensor [ERROR_WORD_SLOTS] of addresses, sources filled in)
+
+
+def register_wait_error_source(name: str, address_fn, take_fn) -> None:
+    if all(n != name for n, _, _ in _wait_error_sources):
+        if len(_wait_error_sources) >= ERROR_WORD_SLOTS:
+            raise KernelError("more kernels with error words than the step's health word has bits")
+        _wait_error_sources.append((name, address_fn, take_fn))
+
+
+def _register_library_sources() -> None:
+    import ctypes
+    from .library import load_library
+    lib = load_library()
+    for name in ("gemm_slab", "gemm_stream_k", "gemm_tcgen05"):
+        word = getattr(lib, f"nhv_{name}_error_word")
+        word.restype, word.argtypes = ctypes.c_void_p, []
+        take = getattr(lib, f"nhv_{name}_error")
+        take.restype, take.argtypes = ctypes.c_int, []
+        register_wait_error_source(name, word, take)
+
+
+def error_word_array(device) -> torch.Tensor:
+    """Device array of the addresses of all error words known so far (zeros where there is none yet).  The
+    array's own address never changes, so a captured step sees words registered after its capture too."""
+    _register_library_sources()
+    device = torch.device(device)
+    entry = _error_word_arrays.get(device)
+    if entry is None:
+        entry = _error_word_arrays[device] = [torch.zeros(ERROR_WORD_SLOTS, dtype=torch.int64, device=device), 0]
+    arr, filled = entry
+    if filled < len(_wait_error_sources):
+        with torch.cuda.device(device):
+            addresses = [fn() or 0 for _, fn, _ in _wait_error_sources[filled:]]
+        arr[filled:len(_wait_error_sources)] = torch.tensor(addresses, dtype=torch.int64)
+        entry[1] = len(_wait_error_sources)
+    return arr
+
+
+def take_wait_errors() -> list[tuple[str, int]]:
+    """(kernel, code) of every bounded wait that ran out since the last call; the words are cleared.
+    Synchronises the device."""
+    _register_library_sources()
+    out = []
+    for name, _, take in _wait_error_sources:
+        code = take()
+        if code != 0:
+            out.append((name, code))
+    return out
+
+
+def raise_wait_errors() -> None:
+    """Raise ``KernelError`` naming the kernels whose bounded waits ran out, if any did."""
+    bad = take_wait_errors()
+    if bad:
+        raise KernelError("a bounded wait ran out in " + ", ".join(f"{n} (code {c})" for n, c in bad) +
+                          ": the kernel gave up and left, and the results of the step are not valid")
+
+
 def sample(out, logits, temperatures, seeds, positions) -> None:
     """out[r] = the token chosen from logits[r] (float32): argmax if temperatures[r] == 0, else the
-    exponential race with noise keyed by (seeds[r], positions[r])."""
+    exponential race with noise keyed by (seeds[r], positions[r]).  ``out`` may have one element more than
+    ``logits`` has rows: it receives the step's health word (bit i set: the i-th registered error word of a
+    kernel with bounded waits is not zero; 0 means that all is well), which the host reads with the tokens."""
     _need_cuda(out, logits, temperatures, seeds, positions)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
     assert temperatures.dtype == torch.float32 and seeds.dtype == torch.int64 and positions.dtype == torch.int32
@@ -494,8 +562,14 @@ def sample(out, logits, temperatures, seeds, positions) -> None:
             _sampler_retired.append(st)      # a captured step may still point at the smaller ones
         st = _sampler_scratch[logits.device] = (torch.zeros(n, dtype=torch.int64, device=logits.device),
                                                 torch.zeros(n, dtype=torch.int32, device=logits.device))
+    words = status = None
+    if out.numel() == rows + 1:
+        words, status = error_word_array(logits.device).data_ptr(), out.data_ptr() + 4 * rows
+    else:
+        assert out.numel() == rows
     call("nhv_sample", out.data_ptr(), logits.data_ptr(), logits.stride(0), temperatures.data_ptr(), seeds.data_ptr(),
-         positions.data_ptr(), rows, logits.shape[1], st[0].data_ptr(), st[1].data_ptr(), stream_ptr())
+         positions.data_ptr(), rows, logits.shape[1], st[0].data_ptr(), st[1].data_ptr(), words, ERROR_WORD_SLOTS, status,
+         stream_ptr())
 
 
 _sampler_scratch: dict = {}
