@@ -23,6 +23,10 @@ class StepItem:
     tokens: list[int]
     start: int                      # tokens of this request already in the cache = position of tokens[0]
     want: list[int] = field(default_factory=list)   # places among `tokens` whose logits are wanted
+    # what the position encoding sees of these tokens, if it is not their index in the request: one number per
+    # token, or one list per position axis of the model (``ModelSpec.position_axes``).  The cache is indexed by
+    # ``start`` whatever stands here.
+    positions: list | None = None
 
 
 @dataclass
@@ -37,7 +41,8 @@ class StepBatch:
     n_seqs: int
     n_logit_rows: int
     token_ids: torch.Tensor         # [T] int32
-    positions: torch.Tensor         # [T] int32, position of each token in its own request
+    positions: torch.Tensor         # [T] int32, position of each token in its own request (axis 0 of position_axes)
+    position_axes: torch.Tensor     # [P, T] int32: every position axis of the model (P = 1 unless the model says otherwise)
     cu_q: torch.Tensor              # [S+1] int32, where each request's tokens start in the packed arrays
     kv_len: torch.Tensor            # [S] int32, tokens of the request in the cache after this step
     q_start: torch.Tensor           # [S] int32, kv_len minus this step's tokens
@@ -64,8 +69,10 @@ def _align(n: int, a: int = 4) -> int:
 
 
 class BatchBuilder:
-    def __init__(self, cache_manager, vocab_size: int, device, max_tokens: int, max_seqs: int, max_pages_per_seq: int):
+    def __init__(self, cache_manager, vocab_size: int, device, max_tokens: int, max_seqs: int, max_pages_per_seq: int,
+                 position_axes: int = 1):
         self.cm = cache_manager
+        self.n_axes = position_axes
         self.vocab = vocab_size
         self.device = torch.device(device)
         self.page_size = cache_manager.page_size
@@ -89,7 +96,7 @@ class BatchBuilder:
             return cached
         off, sections = 0, {}
         for name, n in (("seeds", 2 * R), ("temperatures", R), ("sample_positions", R), ("token_ids", T),
-                        ("positions", T), ("cu_q", S + 1), ("kv_len", S), ("q_start", S),
+                        ("positions", self.n_axes * T), ("cu_q", S + 1), ("kv_len", S), ("q_start", S),
                         ("state_slots", S), ("logit_rows", R)):
             sections[name] = (off, n)
             off += _align(n)
@@ -131,7 +138,7 @@ class BatchBuilder:
             o, n = sec[name]
             return buf[o:o + n]
 
-        tok, pos = view("token_ids"), view("positions")
+        tok, pos_axes = view("token_ids"), view("positions").reshape(self.n_axes, T)
         cu, kvl, qs, st, rows = view("cu_q"), view("kv_len"), view("q_start"), view("state_slots"), view("logit_rows")
         slot_views = [view(f"slots{g}") for g in range(self.n_groups)]
         table_views = [view(f"tables{g}").reshape(S, width) for g in range(self.n_groups)]
@@ -140,7 +147,7 @@ class BatchBuilder:
         # again only if its request or the length of its table differs (a group with a window rewrites always:
         # pages given back change entries without changing the length).
         layout_key = (T, S, R, width)
-        decode_only = n_real > 0 and all(len(it.tokens) == 1 and it.want == [0] for it in items)
+        decode_only = n_real > 0 and all(len(it.tokens) == 1 and it.want == [0] and it.positions is None for it in items)
         keep = decode_only and self._table_rows is not None and self._table_rows[0] == layout_key
         old_rows = self._table_rows[1] if keep else None
         self._table_rows = None          # a build that fails half-way leaves rows nobody has a record of
@@ -185,8 +192,9 @@ class BatchBuilder:
                     page = table[lp]
                     slot_views[g][s] = page * ps + off if page >= 0 else -1
             n = n_real
-            tok[:n], pos[:n], qs[:n], st[:n] = firsts, starts, starts, slots_state
-            kvl[:n] = pos[:n] + 1
+            tok[:n], qs[:n], st[:n] = firsts, starts, slots_state
+            pos_axes[:, :n] = starts
+            kvl[:n] = qs[:n] + 1
             cu[1:n + 1] = np.arange(1, n + 1, dtype=np.int32)
             rows[:n] = cu[:n]
             t = r = n
@@ -210,10 +218,17 @@ class BatchBuilder:
                     raise ValueError(f"request {it.req_id!r}: wanted place {w} is not among its {n} tokens")
                 rows[r] = t + w
                 r += 1
+            if it.positions is not None:
+                given = np.asarray(it.positions, dtype=np.int64)
+                if given.shape not in ((n,), (self.n_axes, n)) or given.min() < 0:
+                    raise ValueError(f"request {it.req_id!r}: positions must be {n} numbers, or {self.n_axes} lists of "
+                                     f"{n}, none negative")
+                pos_axes[:, t:t + n] = given
             if n == 1:
                 # a decoded token: scalars instead of arrays (this is the hot path of every decode step)
                 tok[t] = it.tokens[0]
-                pos[t] = it.start
+                if it.positions is None:
+                    pos_axes[:, t] = it.start
                 for g in range(self.n_groups):
                     table = self.cm.block_table(it.req_id, g)
                     k = min(len(table), width)
@@ -223,7 +238,8 @@ class BatchBuilder:
             else:
                 tok[t:t + n] = it.tokens
                 p = np.arange(it.start, end, dtype=np.int32)
-                pos[t:t + n] = p
+                if it.positions is None:
+                    pos_axes[:, t:t + n] = p
                 for g in range(self.n_groups):
                     table = np.asarray(self.cm.block_table(it.req_id, g), dtype=np.int32)
                     table_views[g][s, :min(len(table), width)] = table[:width]
@@ -234,7 +250,8 @@ class BatchBuilder:
             if keep and old_rows[s] is not None:
                 for tv in table_views:
                     tv[s, :] = -1
-            tok[t], pos[t] = 0, 0
+            tok[t] = 0
+            pos_axes[:, t] = 0
             cu[s + 1] = t + 1
             kvl[s], qs[s], st[s] = 1, 0, -1
             rows[r] = t
@@ -264,7 +281,8 @@ class BatchBuilder:
             samp = dict(temperatures=dev("temperatures").view(torch.float32), seeds=dev("seeds").view(torch.int64),
                         sample_positions=dev("sample_positions"))
         return StepBatch(**samp,
-            n_tokens=T, n_seqs=S, n_logit_rows=R, token_ids=dev("token_ids"), positions=dev("positions"),
+            n_tokens=T, n_seqs=S, n_logit_rows=R, token_ids=dev("token_ids"), positions=dev("positions")[:T],
+            position_axes=dev("positions").view(self.n_axes, T),
             cu_q=dev("cu_q"), kv_len=dev("kv_len"), q_start=dev("q_start"), state_slots=dev("state_slots"),
             logit_rows=dev("logit_rows"), groups=groups, host_cu_q=[int(x) for x in cu[:S + 1]],
             host_kv_len=ends, max_new_tokens=max(lens),

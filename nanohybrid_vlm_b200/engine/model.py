@@ -7,13 +7,13 @@ architecture; what differs is the spec.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 
 import torch
 
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, FixedStateNeed, PagedKVNeed, Part
-from ..parts.embedding import LMHead, TokenEmbedding
-from ..parts.spec import ModelSpec, ParamDecl, PartUse, Source
+from .. import parts as _registered_parts  # noqa: F401  (importing the package registers the built-in parts)
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, BuildEnv, FixedStateNeed, PagedKVNeed, Part
+from ..parts.spec import ModelSpec, ParamDecl, PartUse
 
 
 @dataclass(frozen=True)
@@ -39,20 +39,22 @@ class CausalLM:
             self._uses.append((use, obj))
             return obj
 
-        self.embedding = TokenEmbedding(spec.embedding.spec, env)
-        self._uses.append((spec.embedding, self.embedding))
+        self.embedding = build(EMBEDDINGS, spec.embedding)
         for use in spec.positions:                 # before the layers, so that mixers naming the same spec share them
             self._uses.append((use, env.position(use.spec)))
         self.blocks = []
-        for layer in spec.layers:
-            mixer = build(MIXERS, layer.mixer)
-            mixer_norm = build(NORMS, layer.mixer_norm)
-            ffn = build(FEED_FORWARDS, layer.ffn)
-            ffn_norm = build(NORMS, layer.ffn_norm)
-            self.blocks.append(BLOCKS.get(layer.block.kind)(layer.block, mixer, mixer_norm, ffn, ffn_norm))
+        for i, layer in enumerate(spec.layers):
+            block_cls = BLOCKS.get(layer.block.kind)
+            given = dict(layer.parts)
+            unknown = set(given) - set(block_cls.SLOTS)
+            missing = set(block_cls.SLOTS) - set(given) - set(block_cls.OPTIONAL)
+            if unknown or missing:
+                raise ValueError(f"layer {i}: block {layer.block.kind!r} arranges {sorted(block_cls.SLOTS)}; "
+                                 f"missing {sorted(missing)}, unknown {sorted(unknown)}")
+            built = {name: build(block_cls.SLOTS[name], use) for name, use in layer.parts}
+            self.blocks.append(block_cls(layer.block, built))
         self.final_norm = build(NORMS, spec.final_norm)
-        self.head = LMHead(spec.head.spec, env)
-        self._uses.append((spec.head, self.head))
+        self.head = build(HEADS, spec.head)
         self.positions = list(env._positions.values())
 
     # ------------------------------------------------------------------ tensors
@@ -64,7 +66,7 @@ class CausalLM:
                 if full in seen:
                     raise ValueError(f"two parts declare the tensor {full!r}")
                 seen.add(full)
-                srcs = tuple(Source(use.prefix + s.name, s.row, s.rows) for s in decl.resolved_sources())
+                srcs = tuple(replace(s, name=use.prefix + s.name) for s in decl.resolved_sources())
                 table.append(BoundParam(full, ParamDecl(decl.name, decl.shape, decl.init, decl.storage, srcs), obj,
                                         decl.name))
         return table
@@ -81,7 +83,7 @@ class CausalLM:
         for key, owner in owners.items():
             owner.bind(per_part[key])
         if self.head.tied:
-            self.head.tie(self.embedding.w_weight)
+            self.head.tie(self.embedding)
         self.tensors = tensors
 
     def weight_bytes(self) -> int:
@@ -103,9 +105,11 @@ class CausalLM:
         another run's cache)."""
         needs = []
         for run in self.spec.order:
-            need = self.blocks[run.layer].mixer.cache_need()
+            owner = self.blocks[run.layer].cache_owner
+            need = owner.cache_need() if owner is not None else None
             if run.cache_from is not None:
-                src = self.blocks[self.spec.order[run.cache_from].layer].mixer.cache_need()
+                src_owner = self.blocks[self.spec.order[run.cache_from].layer].cache_owner
+                src = src_owner.cache_need() if src_owner is not None else None
                 if need != src:
                     raise ValueError(f"a run reads the cache of run {run.cache_from}, whose shape differs from its own")
                 need = None
@@ -115,7 +119,7 @@ class CausalLM:
     # ------------------------------------------------------------------ one step
     def forward(self, batch, storage) -> torch.Tensor:
         """Run the batch's tokens through every layer run; returns fp32 logits [wanted rows, vocab]."""
-        h = self.embedding.forward(batch.token_ids)
+        h = self.embedding.forward(batch.token_ids, batch)
         for pos in self.positions:
             h = pos.add_to_embeddings(h, batch)
         residual = None

@@ -56,7 +56,7 @@ class ModelRunner:
                                     poison=config.poison_cache)
         self.builder = BatchBuilder(self.cache, self.vocab_size, self.device,
                                     max_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,
-                                    max_pages_per_seq=self.max_pages_per_seq)
+                                    max_pages_per_seq=self.max_pages_per_seq, position_axes=spec.position_axes)
         # CUDA graphs of the decode step, one per batch-size bucket, captured at first use
         # (the reference captures the same buckets up front, nanovllm/engine/model_runner.py:2560-2594)
         self.graph_buckets = [] if config.enforce_eager else [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)

@@ -6,8 +6,8 @@ dtype, device); it declares its tensors (:class:`~.spec.ParamDecl`), receives th
 ``bind`` and then computes on device tensors.  No part knows which model it is in.
 
 Adding a part: subclass the interface, then ``MIXERS.register("name", Class)`` (or
-``FEED_FORWARDS``, ``NORMS``, ``POSITIONS``, ``BLOCKS``).  A model description refers to
-it as ``part("name", ...)``.
+``FEED_FORWARDS``, ``NORMS``, ``POSITIONS``, ``BLOCKS``, ``EMBEDDINGS``, ``HEADS``).  A model
+description refers to it as ``part("name", ...)``.
 """
 from __future__ import annotations
 
@@ -41,6 +41,8 @@ class Registry:
         return sorted(self._classes)
 
 
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
@@ -159,12 +161,44 @@ class PositionEncoding(Part):
         return h
 
 
-class Block:
-    """The arrangement of a layer's parts.  ``forward`` takes and returns (hidden, residual): the
-    sub-block output not yet added, and the residual stream; residual None means "first layer"."""
+class Embedding(Part):
+    """Token ids to the first hidden states.  ``forward(token_ids [T] int32, batch) -> [T, hidden]``."""
 
-    def __init__(self, spec: PartSpec, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward, ffn_norm: Norm):
-        self.spec, self.mixer, self.mixer_norm, self.ffn, self.ffn_norm = spec, mixer, mixer_norm, ffn, ffn_norm
+    def forward(self, token_ids: torch.Tensor, batch) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Hidden states of the wanted rows (after the final norm) to fp32 logits [rows, vocab].  ``tied`` True: the
+    head owns no table and is handed the embedding part with ``tie`` once the tensors are bound."""
+    tied = False
+
+    def tie(self, embedding: Embedding) -> None:
+        raise NotImplementedError
+
+    def forward(self, rows_hidden: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """The arrangement of a layer's parts.  ``SLOTS`` names the parts this kind of block arranges and the
+    registry each is built from; ``OPTIONAL`` those a layer may leave out.  The model builds them and hands
+    them over as ``parts`` (name -> part; each is also set as an attribute of that name).  ``forward`` takes and
+    returns (hidden, residual): the sub-block output not yet added, and the residual stream; residual None means
+    "first layer".  ``cache_owner`` is the part whose ``cache_need`` decides what a run of this layer keeps
+    between steps (one per layer)."""
+    SLOTS: dict[str, Registry] = {"mixer": MIXERS, "mixer_norm": NORMS, "ffn": FEED_FORWARDS, "ffn_norm": NORMS}
+    OPTIONAL: tuple[str, ...] = ()
+
+    def __init__(self, spec: PartSpec, parts: dict[str, Part]):
+        self.spec = spec
+        self.parts = dict(parts)
+        for name, obj in parts.items():
+            setattr(self, name, obj)
+
+    @property
+    def cache_owner(self) -> Mixer | None:
+        return self.parts.get("mixer")
 
     def forward(self, hidden, residual, batch, cache: CacheView):
         raise NotImplementedError

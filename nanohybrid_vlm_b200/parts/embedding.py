@@ -8,11 +8,11 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import Part
+from .base import EMBEDDINGS, HEADS, Embedding, Head
 from .spec import ParamDecl
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.vocab = int(spec["vocab_size"])
@@ -20,13 +20,13 @@ class TokenEmbedding(Part):
     def params(self):
         return [ParamDecl("weight", (self.vocab, self.env.hidden_size))]
 
-    def forward(self, token_ids):
+    def forward(self, token_ids, batch=None):
         out = self.new(token_ids.numel(), self.env.hidden_size)
         ops.embed(out, self.w_weight, token_ids)
         return out
 
 
-class LMHead(Part):
+class LMHead(Head):
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.vocab = int(spec["vocab_size"])
@@ -35,8 +35,8 @@ class LMHead(Part):
     def params(self):
         return [] if self.tied else [ParamDecl("weight", (self.vocab, self.env.hidden_size))]
 
-    def tie(self, table: torch.Tensor) -> None:
-        self.w_weight = table
+    def tie(self, embedding) -> None:
+        self.w_weight = embedding.w_weight
 
     def streamed_weights(self):
         return [(self.w_weight, 1)]
@@ -45,3 +45,7 @@ class LMHead(Part):
         logits = self.new(rows_hidden.shape[0], self.vocab, dtype=torch.float32)
         ops.linear(logits, rows_hidden, self.w_weight)
         return logits
+
+
+EMBEDDINGS.register("token_embedding", TokenEmbedding)
+HEADS.register("lm_head", LMHead)

@@ -1,9 +1,10 @@
 """Weights from safetensors, by tensor name.
 
 Every ``*.safetensors`` file of the folder is read (sorted, as nanovllm/utils/loader.py:33-46
-does).  The model's tensor table says which checkpoint tensors fill which rows of which
+does).  The model's tensor table says which checkpoint tensors fill which slice of which
 parameter (q/k/v packed into one matrix, gate/up into one; nanovllm/layers/linear.py:102-108,
-153-167).  Tensors are kept in the engine's dtype; a parameter declared "float32" stays
+153-167; a slice may also run along another dimension, be stored transposed, or be one
+entry of a stack).  Tensors are kept in the engine's dtype; a parameter declared "float32" stays
 32-bit and an "int32" table stays integer.  All problems are collected and raised as ONE
 error that lists missing tensors, unexpected tensors and wrong shapes
 (nanovllm/utils/loader.py:231-278 reports the same categories).
@@ -71,15 +72,15 @@ def load_weights(model, model_dir: str) -> dict[str, torch.Tensor]:
                     unexpected.append(name)
                     continue
                 bp, src = wanted[name]
-                want_shape = (src.rows, *bp.decl.shape[1:])
                 got_shape = tuple(f.get_slice(name).get_shape())
-                if got_shape != want_shape:
-                    wrong.append((name, got_shape, want_shape))
+                part = src.to_slice(torch.empty(got_shape, device="meta"), bp.decl.shape)
+                if part is None:
+                    wrong.append((name, got_shape, src.checkpoint_shape(bp.decl.shape)))
                     seen.add(name)
                     continue
-                t = f.get_tensor(name)
+                t = src.to_slice(f.get_tensor(name), bp.decl.shape)
                 dst = tensors[bp.name]
-                dst.narrow(0, src.row, src.rows).copy_(t.to(dst.dtype) if t.dtype != dst.dtype else t)
+                dst.narrow(src.dim, src.row, src.rows).copy_(t.to(dst.dtype) if t.dtype != dst.dtype else t)
                 seen.add(name)
     missing = [n for n in wanted if n not in seen]
     if missing or unexpected or wrong:

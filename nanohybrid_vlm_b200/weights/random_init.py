@@ -24,16 +24,32 @@ def tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF
 
 
+def _normal(std: float, mean: float = 0.0):
+    def draw(shape, gen, device):
+        t = torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen)
+        return t + mean if mean else t
+    return draw
+
+
+# init kind (``ParamDecl.init``) -> function (shape, generator, device) -> float32 tensor
+INITS = {
+    "normal": _normal(0.02),
+    "norm": _normal(0.01, 1.0),
+    "zeros_noise": _normal(0.01),
+    "zeros": lambda shape, gen, device: torch.zeros(shape, dtype=torch.float32, device=device),
+}
+
+
+def register_init(kind: str, draw) -> None:
+    """Another way of filling a tensor in the random-weights mode: ``draw(shape, generator, device)`` returns
+    a float32 tensor; parts name it in ``ParamDecl.init``."""
+    INITS[kind] = draw
+
+
 def _draw(shape, init: str, gen: torch.Generator, device) -> torch.Tensor:
-    if init == "normal":
-        return torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=gen)
-    if init == "norm":
-        return 1.0 + torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, 0.01, generator=gen)
-    if init == "zeros_noise":
-        return torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, 0.01, generator=gen)
-    if init == "zeros":
-        return torch.zeros(shape, dtype=torch.float32, device=device)
-    raise ValueError(f"unknown init kind {init!r}")
+    if init not in INITS:
+        raise ValueError(f"unknown init kind {init!r}; known: {sorted(INITS)}")
+    return INITS[init](tuple(shape), gen, device)
 
 
 def random_checkpoint(model, seed: int, dtype: torch.dtype) -> dict[str, torch.Tensor]:
@@ -42,7 +58,7 @@ def random_checkpoint(model, seed: int, dtype: torch.dtype) -> dict[str, torch.T
     for bp in model.param_table():
         for src in bp.decl.sources:
             gen = torch.Generator(device="cpu").manual_seed(tensor_seed(seed, src.name))
-            t = _draw((src.rows, *bp.decl.shape[1:]), bp.decl.init, gen, "cpu")
+            t = _draw(src.checkpoint_shape(bp.decl.shape), bp.decl.init, gen, "cpu")     # in the file's own layout
             out[src.name] = t.to(storage_dtype(bp.decl.storage, dtype)).contiguous()
     return out
 
@@ -78,7 +94,8 @@ def materialize_random(model, seed: int) -> dict[str, torch.Tensor]:
         dst = torch.empty(bp.decl.shape, dtype=storage_dtype(bp.decl.storage, model.dtype), device=model.device)
         for src in bp.decl.sources:
             gen = torch.Generator(device=model.device).manual_seed(tensor_seed(seed, src.name))
-            dst.narrow(0, src.row, src.rows).copy_(_draw((src.rows, *bp.decl.shape[1:]), bp.decl.init, gen, model.device))
+            t = _draw(src.checkpoint_shape(bp.decl.shape), bp.decl.init, gen, model.device)
+            dst.narrow(src.dim, src.row, src.rows).copy_(src.to_slice(t, bp.decl.shape))
         tensors[bp.name] = dst
     model.bind(tensors)
     return tensors

@@ -130,7 +130,7 @@ def test_embedding_and_head_parts():
     assert torch.equal(emb.forward(ids.cuda()).cpu(), table[ids.long()])
     head = LMHead(part("lm_head", vocab_size=101, tied=True), env)
     assert head.params() == []
-    head.tie(emb.w_weight)
+    head.tie(emb)
     x = torch.randn(3, 48, generator=torch.Generator().manual_seed(5))
     torch.testing.assert_close(head.forward(x.cuda()).cpu(), x @ table.t(), rtol=1e-5, atol=1e-5)
 
@@ -641,3 +641,223 @@ def test_routing_learnt_positions_another_norm_and_another_block_register_build_
         POSITIONS.unregister("learnt")
         NORMS.unregister("mean_centred")
         BLOCKS.unregister("parallel")
+
+
+# ------------------------------------------------------------------------------------------------ another block, embedding, head, positions and checkpoint layout
+
+SANDWICH = dict(architectures=["ToySandwichLM"], model_type="toy_sandwich", hidden_size=40, vocab_size=71,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=16, expert_size=24, num_experts=3,
+                rms_norm_eps=1e-5, rope_theta=500.0, max_position_embeddings=96, logit_cap=0.3, torch_dtype="float32")
+
+
+def register_sandwich_toy():
+    """Parts that the engine's own files know nothing of, all defined here: a block kind with four norms (one
+    before and one behind each sub-block) and no residual carried apart; an embedding with a scale; a head with
+    a bias and a soft cap; a position table with two axes whose positions the caller gives; a feed-forward whose
+    checkpoint stores its matrices transposed, split by columns, and one tensor per expert."""
+    from nanohybrid_vlm_b200.config import ModelConfig, register_architecture
+    from nanohybrid_vlm_b200.parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Block,
+                                           Embedding, FeedForward, Head, LayerRun, LayerSpec, ModelSpec, ParamDecl,
+                                           PartUse, PositionEncoding, Source, part)
+    from nanohybrid_vlm_b200.weights.random_init import register_init
+
+    class SandwichBlock(Block):
+        SLOTS = {"mixer": MIXERS, "mixer_norm": NORMS, "mixer_post_norm": NORMS,
+                 "ffn": FEED_FORWARDS, "ffn_norm": NORMS, "ffn_post_norm": NORMS}
+        OPTIONAL = ("ffn", "ffn_norm", "ffn_post_norm")              # a layer may be a mixer alone
+
+        def forward(self, hidden, residual, batch, cache):
+            stream = hidden if residual is None else residual + hidden
+            a = self.mixer_post_norm.forward(self.mixer.forward(self.mixer_norm.forward(stream), batch, cache))
+            if "ffn" not in self.parts:
+                return a, stream
+            stream = stream + a
+            return self.ffn_post_norm.forward(self.ffn.forward(self.ffn_norm.forward(stream), batch)), stream
+
+    class ScaledEmbedding(Embedding):
+        def params(self):
+            return [ParamDecl("weight", (int(self.spec["vocab_size"]), self.env.hidden_size))]
+
+        def forward(self, token_ids, batch):
+            return self.w_weight[token_ids.long()] * float(self.spec["scale"])
+
+    class CappedHead(Head):
+        def params(self):
+            V = int(self.spec["vocab_size"])
+            return [ParamDecl("weight", (V, self.env.hidden_size)), ParamDecl("bias", (V,), init="tenths")]
+
+        def forward(self, rows_hidden):
+            cap = float(self.spec["cap"])
+            return cap * torch.tanh((rows_hidden.float() @ self.w_weight.float().t() + self.w_bias.float()) / cap)
+
+    class TwoAxisPositions(PositionEncoding):
+        def params(self):
+            n = int(self.spec["max_position"])
+            return [ParamDecl("rows.weight", (n, self.env.hidden_size)), ParamDecl("cols.weight", (n, self.env.hidden_size))]
+
+        def add_to_embeddings(self, h, batch):
+            assert batch.position_axes.shape == (2, h.shape[0])
+            return h + self.w_rows_weight[batch.position_axes[0].long()] + self.w_cols_weight[batch.position_axes[1].long()]
+
+    class StackedExperts(FeedForward):
+        """Every token goes to the expert with the largest router score.  The up matrices are one parameter
+        [E, I, H] filled from one checkpoint tensor per expert, each stored transposed ([H, I]); the down matrices
+        one parameter [H, E * I] filled column block by column block."""
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.E, self.I = int(spec["num_experts"]), int(spec["expert_size"])
+
+        def params(self):
+            H, E, I = self.env.hidden_size, self.E, self.I
+            return [ParamDecl("router.weight", (E, H)),
+                    ParamDecl("up", (E, I, H), sources=tuple(Source(f"experts.{e}.up_t", e, 1, transpose=True, squeeze=True) for e in range(E))),
+                    ParamDecl("down", (H, E * I), sources=tuple(Source(f"experts.{e}.down", e * I, I, 1) for e in range(E)))]
+
+        def forward(self, x, batch):
+            xf = x.float()
+            e = (xf @ self.w_router_weight.float().t()).argmax(-1)                    # [T]
+            up = torch.einsum("tih,th->ti", self.w_up.float()[e], xf)
+            down = self.w_down.float().view(-1, self.E, self.I).permute(1, 0, 2)[e]    # [T, H, I]
+            return torch.einsum("thi,ti->th", down, torch.relu(up)).to(x.dtype)
+
+    register_init("tenths", lambda shape, gen, device: torch.empty(shape, dtype=torch.float32, device=device).uniform_(-0.1, 0.1, generator=gen))
+    BLOCKS.register("sandwich", SandwichBlock, replace=True)
+    EMBEDDINGS.register("scaled_embedding", ScaledEmbedding, replace=True)
+    HEADS.register("capped_head", CappedHead, replace=True)
+    POSITIONS.register("two_axis", TwoAxisPositions, replace=True)
+    FEED_FORWARDS.register("stacked_experts", StackedExperts, replace=True)
+
+    def parse(raw):
+        cfg = ModelConfig(architecture="ToySandwichLM", model_type=raw["model_type"], vocab_size=raw["vocab_size"],
+                          hidden_size=raw["hidden_size"], max_position_embeddings=raw["max_position_embeddings"],
+                          dtype=torch.float32, eos_token_id=None)
+        object.__setattr__(cfg, "raw", raw)
+        return cfg
+
+    def build(cfg):
+        raw = cfg.raw
+        H, V = raw["hidden_size"], raw["vocab_size"]
+        norm = part("rmsnorm", width=H, eps=raw["rms_norm_eps"])
+        rope = part("rope", theta=raw["rope_theta"], rotary_dim=raw["head_dim"], max_position=raw["max_position_embeddings"])
+        attn = part("gqa_attention", num_heads=raw["num_attention_heads"], num_kv_heads=raw["num_key_value_heads"],
+                    head_dim=raw["head_dim"], qk_norm_eps=raw["rms_norm_eps"], position=rope)
+        ffn = part("stacked_experts", num_experts=raw["num_experts"], expert_size=raw["expert_size"])
+
+        def use(p, i, name):
+            return PartUse(p, f"layers.{i}.{name}.")
+
+        full = LayerSpec(part("sandwich"), mixer=use(attn, 0, "attn"), mixer_norm=use(norm, 0, "pre_attn"),
+                         mixer_post_norm=use(norm, 0, "post_attn"), ffn=use(ffn, 0, "ffn"),
+                         ffn_norm=use(norm, 0, "pre_ffn"), ffn_post_norm=use(norm, 0, "post_ffn"))
+        mixer_only = LayerSpec(part("sandwich"), mixer=use(attn, 1, "attn"), mixer_norm=use(norm, 1, "pre_attn"),
+                               mixer_post_norm=use(norm, 1, "post_attn"))
+        return ModelSpec(architecture="ToySandwichLM", hidden_size=H, vocab_size=V, max_position=raw["max_position_embeddings"],
+                         embedding=PartUse(part("scaled_embedding", vocab_size=V, scale=H ** 0.5), "embed."),
+                         positions=(PartUse(part("two_axis", max_position=raw["max_position_embeddings"]), "positions."),),
+                         position_axes=2, layers=(full, mixer_only), order=(LayerRun(0), LayerRun(1)),
+                         final_norm=PartUse(norm, "final_norm."),
+                         head=PartUse(part("capped_head", vocab_size=V, cap=raw["logit_cap"]), "head."))
+
+    register_architecture("ToySandwichLM", model_types=("toy_sandwich",), parse_config=parse, build_spec=build, replace=True)
+
+
+def sandwich_plain_logits(w, tokens, rows, cols):
+    raw, T = SANDWICH, len(tokens)
+    nq, nkv, d, eps, H = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], raw["rms_norm_eps"], raw["hidden_size"]
+    cos, sin = plain.rope_table(d, raw["max_position_embeddings"], raw["rope_theta"])
+    rows, cols = torch.tensor(rows), torch.tensor(cols)
+    stream = w["embed.weight"][torch.tensor(tokens)] * H ** 0.5 + w["positions.rows.weight"][rows] + w["positions.cols.weight"][cols]
+
+    def attention(x, p):
+        q = plain.linear(x, w[p + "q_proj.weight"]).view(T, nq, d)
+        k = plain.linear(x, w[p + "k_proj.weight"]).view(T, nkv, d)
+        v = plain.linear(x, w[p + "v_proj.weight"]).view(T, nkv, d)
+        q = plain.apply_rope(plain.rms_norm(q, w[p + "q_norm.weight"], eps), cos[rows], sin[rows])
+        k = plain.apply_rope(plain.rms_norm(k, w[p + "k_norm.weight"], eps), cos[rows], sin[rows])
+        return plain.linear(plain.causal_attention(q, k, v, d ** -0.5).reshape(T, nq * d), w[p + "o_proj.weight"])
+
+    a = plain.rms_norm(attention(plain.rms_norm(stream, w["layers.0.pre_attn.weight"], eps), "layers.0.attn."),
+                       w["layers.0.post_attn.weight"], eps)
+    stream = stream + a
+    x = plain.rms_norm(stream, w["layers.0.pre_ffn.weight"], eps)
+    out = []
+    for t in range(T):
+        e = int((w["layers.0.ffn.router.weight"] @ x[t]).argmax())
+        up = w[f"layers.0.ffn.experts.{e}.up_t"].t()                  # stored [H, I]
+        out.append(w[f"layers.0.ffn.experts.{e}.down"] @ torch.relu(up @ x[t]))
+    stream = stream + plain.rms_norm(torch.stack(out), w["layers.0.post_ffn.weight"], eps)
+    a = plain.rms_norm(attention(plain.rms_norm(stream, w["layers.1.pre_attn.weight"], eps), "layers.1.attn."),
+                       w["layers.1.post_attn.weight"], eps)
+    x = plain.rms_norm(a + stream, w["final_norm.weight"], eps)
+    cap = raw["logit_cap"]
+    return cap * torch.tanh((x @ w["head.weight"].t() + w["head.bias"]) / cap)
+
+
+def test_a_block_with_post_norms_a_scaled_embedding_a_capped_head_given_positions_and_another_checkpoint_layout(tmp_path):
+    from safetensors.torch import load_file
+    from nanohybrid_vlm_b200.config import ARCHITECTURES, Config
+    from nanohybrid_vlm_b200.engine import ModelRunner, StepItem
+    from nanohybrid_vlm_b200.parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, POSITIONS
+    from nanohybrid_vlm_b200.weights import WeightError, write_random_model
+    register_sandwich_toy()
+    try:
+        raw = SANDWICH
+        d = write_random_model(str(tmp_path / "sandwich"), raw, seed=13)
+        w = load_file(f"{d}/model.safetensors")
+        # the file is written in the checkpoint's own layout: transposed up matrices, one pair of tensors per expert
+        assert w["layers.0.ffn.experts.2.up_t"].shape == (raw["hidden_size"], raw["expert_size"])
+        assert w["layers.0.ffn.experts.0.down"].shape == (raw["hidden_size"], raw["expert_size"])
+        assert "layers.1.ffn.router.weight" not in w and "layers.1.post_attn.weight" in w and w["head.bias"].abs().max() <= 0.1
+        runner = ModelRunner(Config(d, kvcache_block_size=8, num_kvcache_blocks=24, max_num_seqs=3,
+                                    max_num_batched_tokens=64, max_model_len=96, enforce_eager=True))
+        assert runner.builder.n_axes == 2
+        rng = np.random.default_rng(5)
+        reqs = {"a": rng.integers(0, raw["vocab_size"], 37).tolist(), "b": rng.integers(0, raw["vocab_size"], 20).tolist()}
+        # positions that are not the index in the request: a grid walked row by row, and an offset start
+        rows = {"a": [3 + i // 6 for i in range(37)], "b": [50 + i for i in range(20)]}
+        cols = {"a": [i % 6 for i in range(37)], "b": [7] * 20}
+        ref = {r: sandwich_plain_logits(w, reqs[r], rows[r], cols[r]) for r in reqs}
+        used = {int((w["layers.0.ffn.router.weight"] @ x).argmax()) for x in torch.randn(64, raw["hidden_size"], generator=torch.Generator().manual_seed(0))}
+        assert len(used) > 1
+        cuts = {"a": [19, 1, 17], "b": [2, 17, 1]}
+        at, got = {"a": 0, "b": 0}, {"a": [], "b": []}
+        for step in range(3):
+            items = []
+            for r in reqs:
+                n = cuts[r][step]
+                runner.cache.allocate(r, at[r] + n)
+                items.append(StepItem(r, reqs[r][at[r]:at[r] + n], at[r], list(range(n)),
+                                      positions=[rows[r][at[r]:at[r] + n], cols[r][at[r]:at[r] + n]]))
+                at[r] += n
+            logits = runner.step(items).cpu()
+            k = 0
+            for it in items:
+                got[it.req_id].append(logits[k:k + len(it.tokens)])
+                k += len(it.tokens)
+        for r in reqs:
+            torch.testing.assert_close(torch.cat(got[r]), ref[r], rtol=1e-4, atol=2e-5)
+        with pytest.raises(ValueError, match="positions must be"):
+            runner.cache.allocate("c", 3)
+            runner.step([StepItem("c", [1, 2, 3], 0, [], positions=[[0, 1, 2]] * 3)])
+        # a checkpoint tensor in another layout than the declared one is a wrong shape, named with both
+        from safetensors.torch import save_file
+        w["layers.0.ffn.experts.1.up_t"] = w["layers.0.ffn.experts.1.up_t"].t().contiguous()
+        save_file(w, f"{d}/model.safetensors")
+        with pytest.raises(WeightError, match=r"experts\.1\.up_t: checkpoint \(24, 40\) but the model wants \(40, 24\)"):
+            ModelRunner(Config(d, kvcache_block_size=8, num_kvcache_blocks=24, max_num_seqs=3, max_num_batched_tokens=64,
+                               max_model_len=96, enforce_eager=True))
+        with pytest.raises(ValueError, match="arranges"):
+            from nanohybrid_vlm_b200.engine.model import CausalLM
+            from nanohybrid_vlm_b200.parts import LayerSpec, PartUse, part
+            spec = ARCHITECTURES.resolve(raw).build_spec(ARCHITECTURES.resolve(raw).parse_config(raw))
+            bad = LayerSpec(part("prenorm_residual"), mixer=spec.layers[0].mixer, mixer_norm=spec.layers[0].mixer_norm,
+                            gate=spec.layers[0].ffn_norm)
+            import dataclasses
+            CausalLM(dataclasses.replace(spec, layers=(bad,), order=spec.order[:1]), torch.float32, "cuda")
+    finally:
+        ARCHITECTURES.unregister("ToySandwichLM")
+        BLOCKS.unregister("sandwich")
+        EMBEDDINGS.unregister("scaled_embedding")
+        HEADS.unregister("capped_head")
+        POSITIONS.unregister("two_axis")
+        FEED_FORWARDS.unregister("stacked_experts")
