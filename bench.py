@@ -1,6 +1,8 @@
 """Benchmark of the engine's decode and prefill steps on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload 0.6b|32b      the baseline's other two workloads, through the Python entry point
+    python bench.py --breakdown              where a decode step's and a prefill's time goes, by kind of kernel
 
 The default run has the layer sizes of the Qwen3-8B-shaped configuration (36 layers, width 4096,
 32/8 heads of 128, feed-forward 12288, vocabulary 151936), bfloat16, random weights, batch 8,
@@ -37,6 +39,11 @@ CONFIG_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_
                  num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
                  vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
                  max_position_embeddings=40960, torch_dtype="bfloat16", hidden_act="silu", attention_bias=False)
+# the other two shapes that the baseline names (random weights, seeds 3 and 4), run with --workload
+CONFIG_06B = dict(CONFIG_8B, hidden_size=1024, num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
+                  intermediate_size=3072, tie_word_embeddings=True)
+CONFIG_32B = dict(CONFIG_8B, hidden_size=5120, num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8,
+                  intermediate_size=25600)
 FULL_LAYERS = 36
 PROMPT_LEN = 2048
 CONTEXT = 4096
@@ -274,6 +281,208 @@ def bench_ours(args) -> dict:
     }
 
 
+def percentile(values, q: float) -> float:
+    v = sorted(values)
+    return v[min(len(v) - 1, int(q * len(v)))] if v else 0.0
+
+
+def bench_workload(args) -> dict:
+    """The baseline's other two workloads, driven as a user would: ``LLM.add_request`` for every request, then
+    ``LLM.step`` until all are done (host token lists in, chosen tokens back on the host every step).
+
+    0.6b: Qwen3-0.6B-shaped, 256 requests with uniform-random prompts of 64 to 4,096 tokens and 256 new tokens
+    each under continuous batching.  32b: Qwen3-32B-shaped, 32 requests of 4,096 tokens, 128 new tokens each.
+    ``value`` is generated tokens per second over the steps in which every live request decodes (the steady
+    state that the roofline describes); ``run`` has the whole run, prompts included."""
+    import torch
+
+    from nanohybrid_vlm_b200 import LLM, SamplingParams
+
+    if args.workload == "0.6b":
+        cfg, seed, name = dict(CONFIG_06B), 3, "Qwen3-0.6B-shaped"
+        n_req, new, context, max_seqs = 256, 256, 8192, 256
+        gen = torch.Generator().manual_seed(seed)
+        lens = torch.randint(64, 4097, (n_req,), generator=gen).tolist()
+        what = "256 requests, prompts U[64,4096], 256 new tokens, continuous batching"
+    else:
+        cfg, seed, name = dict(CONFIG_32B), 4, "Qwen3-32B-shaped"
+        n_req, new, context, max_seqs = 32, 128, 8192, 32
+        gen = torch.Generator().manual_seed(seed)
+        lens = [4096] * n_req
+        what = "batch 32, 4,096-token prompts, 128 new tokens"
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers if args.layers != FULL_LAYERS else full_layers
+    cfg["num_hidden_layers"] = layers
+    if args.requests:
+        n_req, lens = args.requests, lens[:args.requests]
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist() for n in lens]
+    pk = peaks()
+    nums = model_numbers(cfg, layers)
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(cfg, f)
+        llm = LLM(d, random_weights_seed=seed, kvcache_block_size=PAGE, max_model_len=context, max_num_seqs=max_seqs,
+                  max_num_batched_tokens=16384, seed=seed, enforce_eager=args.eager, enable_prefix_cache=False)
+    params = SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True)
+    # warm-up: one short request through prefill and the decode graph of the smallest bucket
+    llm.generate([prompts[0][:64]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True), use_tqdm=False)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler()
+    sampler.start()
+    for p in prompts:
+        llm.add_request(p, params)
+    records = []                               # (prefill tokens, decode tokens, seconds, live cache tokens after the step)
+    h0, d0 = llm.h2d_bytes, llm.d2h_bytes
+    from nanohybrid_vlm_b200.kernels import library as klib
+    klib.LAUNCHES = 0
+    t_start = time.perf_counter()
+    while not llm.is_finished():
+        t0 = time.perf_counter()
+        _, stats = llm.step()
+        dt = time.perf_counter() - t0
+        live = sum(s.num_cached_tokens for s in llm.scheduler.running) + sum(s.num_cached_tokens for s in llm.scheduler.waiting)
+        records.append((stats.num_prefill_tokens, stats.num_decode_tokens, dt, live))
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t_start
+    clocks = sampler.stop()
+    out_tokens = n_req * new
+    most = max(r[1] for r in records)
+    steady = [r for r in records if r[0] == 0 and r[1] == most]         # every live request decodes, the batch is full
+    if len(steady) > 8:
+        steady = steady[2:]                                             # the first ones capture the graph of their bucket
+    ms = [r[2] * 1e3 for r in steady]
+    mean_ms = sum(ms) / len(ms)
+    mean_live = sum(r[3] for r in steady) / len(steady)
+    # every layer's matrices and the head's table once (a tied table is the same bytes; the embedding reads only the
+    # batch's rows), plus the keys and values of the live requests
+    step_bytes = nums["weight_bytes"] + mean_live * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (mean_ms * 1e-3) / 1e9
+    value = most / mean_ms * 1e3
+    metrics = llm.get_completed_request_metrics()
+    ttft = [m.ttft_ms for m in metrics if m.ttft_ms is not None]
+    return {
+        "metric": f"decode tok/s in the steady state of the workload ({name} bf16: {what})",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": len(steady), "warmup": 1,
+        "ms_per_step": round(mean_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": f"synthetic (uniform-random token ids, random weights N(0,0.02), seed {seed})", "impl": "ours",
+        "config": {"model": name, "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": cfg["tie_word_embeddings"],
+                   "global_batch": most, "requests": n_req, "new_tokens": new, "seq_len": context, "page_size": PAGE,
+                   "parallelism": "single-gpu", "l2": "inputs_exceed_l2 (weights and cache per step, no flush)",
+                   "peaks": pk["source"], "cache_pages": llm.config.num_kvcache_blocks,
+                   "decode_weight_copy": bool(llm.config.decode_weight_copy)},
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int((llm.h2d_bytes - h0) / len(records)),
+                "d2h_bytes_per_step": int((llm.d2h_bytes - d0) / len(records))},
+        "gpu_launches": int(klib.LAUNCHES),
+        "run": {"seconds": round(wall, 3), "steps": len(records), "generated_tokens": out_tokens,
+                "generated_tok_s": round(out_tokens / wall, 1),
+                "prompt_tokens": sum(lens), "all_tok_s": round((out_tokens + sum(lens)) / wall, 1),
+                "preemptions": llm.scheduler.num_preemptions,
+                "ttft_ms_p50": round(percentile(ttft, 0.5), 1), "ttft_ms_max": round(max(ttft), 1)},
+        "step_ms": {"p50": round(percentile(ms, 0.5), 3), "p90": round(percentile(ms, 0.9), 3), "p99": round(percentile(ms, 0.99), 3),
+                    "mean_live_cache_tokens": int(mean_live)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "clocks": clocks,
+    }
+
+
+def bench_breakdown(args) -> dict:
+    """Where the time of a decode step (batch 8, context 2,048) and of a 2,048-token prefill goes, by kind of
+    kernel: CUDA events around every launch of an EAGER run with few layers (default 2; the layers are alike).
+    No profiler is needed.  In an eager run every launch also waits for the host, so a kind's time includes the
+    gaps before its launches: compare the shares within a column, and the prefill column (long kernels) more
+    than the decode column (kernels of a few microseconds)."""
+    import torch
+
+    from nanohybrid_vlm_b200 import LLM
+    from nanohybrid_vlm_b200.engine import StepItem
+    from nanohybrid_vlm_b200.kernels import ops
+
+    layers = args.layers if args.layers != FULL_LAYERS else 2
+    cfg = dict(CONFIG_8B, num_hidden_layers=layers)
+    gen = torch.Generator().manual_seed(SEED)
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(cfg, f)
+        llm = LLM(d, random_weights_seed=SEED, kvcache_block_size=PAGE, num_kvcache_blocks=10 * (CONTEXT // PAGE),
+                  max_model_len=CONTEXT, max_num_seqs=8, max_num_batched_tokens=8192, seed=SEED, enforce_eager=True)
+    runner = llm.model_runner
+    kinds = {"linear": "gemm", "swiglu_first_half": "gemm", "rmsnorm": "norm", "qk_norm_rope_store": "rope_store",
+             "attention": "attention", "attention_decode_fused": "attention", "silu_mul": "silu", "embed": "embed",
+             "sample": "sample", "to_f32": "convert"}
+    events, depth = [], [0]
+    stock = {name: getattr(ops, name) for name in kinds}
+
+    def timed(name, fn):
+        def call(*a, **kw):
+            if depth[0]:                         # a launch inside a launch that is timed already
+                return fn(*a, **kw)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            depth[0] += 1
+            e0.record()
+            try:
+                return fn(*a, **kw)
+            finally:
+                e1.record()
+                depth[0] -= 1
+                events.append((kinds[name], e0, e1))
+        return call
+
+    def measure(step_fn, repeats):
+        for _ in range(3):
+            step_fn()
+        torch.cuda.synchronize()
+        for name, fn in stock.items():
+            setattr(ops, name, timed(name, fn))
+        events.clear()
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        try:
+            w0.record()
+            for _ in range(repeats):
+                step_fn()
+            w1.record()
+            torch.cuda.synchronize()
+        finally:
+            for name, fn in stock.items():
+                setattr(ops, name, fn)
+        total = {}
+        for kind, e0, e1 in events:
+            total[kind] = total.get(kind, 0.0) + e0.elapsed_time(e1) * 1e3 / repeats
+        out = {k: round(v, 1) for k, v in sorted(total.items(), key=lambda kv: -kv[1])}
+        out["step_us"] = round(w0.elapsed_time(w1) * 1e3 / repeats, 1)
+        return out
+
+    prompts = [torch.randint(0, cfg["vocab_size"], (PROMPT_LEN,), generator=gen).tolist() for _ in range(8)]
+
+    def prefill():
+        runner.cache.allocate("pf", PROMPT_LEN)
+        runner.step([StepItem("pf", prompts[0], 0, [PROMPT_LEN - 1])])
+        runner.cache.free("pf")
+
+    pf = measure(prefill, 3)
+    lens = {}
+    for i, p in enumerate(prompts):
+        runner.cache.allocate(i, PROMPT_LEN + 1)
+        runner.step([StepItem(i, p, 0, [])])
+        lens[i] = PROMPT_LEN
+
+    def decode():
+        items = []
+        for i in lens:
+            runner.cache.allocate(i, lens[i] + 1)
+            items.append(StepItem(i, [1], lens[i], [0]))
+            lens[i] += 1
+        runner.run(items, [(0.0, 1, lens[i]) for i in lens])
+
+    dec = measure(decode, 8)
+    return {"breakdown_us": {"decode_b8_ctx2048": dec, "prefill_2048": pf}, "layers": layers, "model": "Qwen3-8B-shaped",
+            "dtype": "bf16", "how": "CUDA events around each launch of an eager run; the gaps before a kind's launches count "
+            "toward it; the head, the sampler and the embedding run once per step, the rest once per layer"}
+
+
 def _unavailable(reason: str) -> dict:
     return {"impl": "reference", "unavailable": " ".join(str(reason).split())[:300]}
 
@@ -430,13 +639,26 @@ def main() -> int:
                     help="run only the decode steps or only the prefill step (profiling); prints no JSON line")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS,
                     help="fewer layers than the full model (sizes of a layer unchanged); recorded in config")
+    ap.add_argument("--workload", default="8b", choices=["8b", "0.6b", "32b"],
+                    help="8b: the headline line; 0.6b / 32b: the baseline's other workloads through LLM.add_request / step")
+    ap.add_argument("--requests", type=int, default=0, help="fewer requests than the workload names (trying it out)")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="time by kind of kernel in an eager run with --layers layers (default 2); prints one JSON line")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (N=1 only)")
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    out = bench_reference(args) if args.impl == "reference" else bench_ours(args)
+    if args.breakdown:
+        out = bench_breakdown(args)
+    elif args.workload != "8b":
+        if args.impl == "reference":
+            out = _unavailable("the reference arm is run for the headline workload only")
+        else:
+            out = bench_workload(args)
+    else:
+        out = bench_reference(args) if args.impl == "reference" else bench_ours(args)
     if out is not None:
         print(json.dumps(out))
     return 0

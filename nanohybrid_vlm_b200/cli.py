@@ -3,6 +3,7 @@
     python -m nanohybrid_vlm_b200.cli generate --model DIR --prompt-ids 1,2,3 [--prompt-ids 4,5] [options]
     python -m nanohybrid_vlm_b200.cli make-random --model DIR --config CONFIG.json --seed N
     python -m nanohybrid_vlm_b200.cli replay --model DIR --dtype D --out DIR --max-tokens N < trace.jsonl
+    python -m nanohybrid_vlm_b200.cli bench [--workload 8b|0.6b|32b] [--breakdown] [...]       (bench.py's options)
 
 Options carry the names of the engine's options (and, where the reference has them, its names:
 nanovllm/config.py:9-152, nanovllm/sampling_params.py:5-15), with dashes for underscores.
@@ -72,10 +73,20 @@ def cmd_replay(args, rest) -> int:
     os.execv(sys.executable, [sys.executable, script, *rest])
 
 
+def cmd_bench(rest) -> int:
+    script = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+    if not os.path.isfile(script):
+        print(f"bench.py is not beside the package ({script})", file=sys.stderr)
+        return 2
+    os.execv(sys.executable, [sys.executable, script, *rest])
+
+
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if argv and argv[0] == "replay":
         return cmd_replay(None, argv[1:])
+    if argv and argv[0] == "bench":
+        return cmd_bench(argv[1:])
     ap = argparse.ArgumentParser(prog="nanohybrid_vlm_b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="command", required=True)
@@ -93,6 +104,7 @@ def main(argv=None) -> int:
     m.add_argument("--config", required=True, help="a config.json to copy the sizes from")
     m.add_argument("--seed", type=int, default=0)
     sub.add_parser("replay", help="trace replay; arguments as bin/trace_run")
+    sub.add_parser("bench", help="the benchmark program; arguments as bench.py")
     args = ap.parse_args(argv)
     return {"generate": cmd_generate, "make-random": cmd_make_random}[args.command](args)
 
