@@ -13,7 +13,7 @@ import weakref
 
 import torch
 
-from . import attention_mma, attention_tcgen05, library
+from . import attention_decode, attention_mma, attention_tcgen05, library
 from .library import KernelError, call
 
 F32, BF16 = 0, 1
@@ -141,6 +141,39 @@ def attention(out, q, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int,
 
 
 FUSE_DECODE_QK = True             # tests switch it off to compare with the two-kernel form
+USE_TMA_DECODE = True             # tests switch it off to reach the mma.sync decode kernel at the same shapes
+
+_decode_scratch: dict = {}
+
+
+def _tma_decode_scratch(device, head_dim: int, blocks: int):
+    """Partial results of the decode kernel's split requests: two slots per block, kept for the life of the
+    process (every launch writes a slot before any block reads it)."""
+    key = (device, head_dim)
+    st = _decode_scratch.get(key)
+    if st is None:
+        st = _decode_scratch[key] = (torch.empty(blocks * 2 * 16 * head_dim, dtype=torch.float32, device=device),
+                                     torch.empty(blocks * 2 * 16 * 2, dtype=torch.float32, device=device))
+    return st
+
+
+def _attention_decode_tma(out, q, qkv, kv_pages, block_table, batch_cu_q, batch_kv_len, n_seqs: int, nq: int, nkv: int,
+                          head_dim: int, scale: float, window: int, q_weight=None, k_weight=None, cos_sin=None,
+                          positions=None, slot_mapping=None, rotary_dim: int = 0, eps: float = 0.0,
+                          weight_offset: float = 0.0, store: bool = False) -> None:
+    launch, blocks = attention_decode.get(head_dim)
+    n_pages, two, h, page_size, d = kv_pages.shape
+    group = nq // nkv
+    head_blocks = nkv * -(-group // 16)
+    part_o, part_ml = _tma_decode_scratch(out.device, head_dim, blocks)
+    counters = _decode_counters(out.device, n_seqs * head_blocks)
+    library.LAUNCHES += 1
+    launch(_ptr(q), 0 if q is None else q.stride(0), _ptr(qkv), 0 if qkv is None else qkv.stride(0), out.data_ptr(),
+           out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), batch_cu_q.data_ptr(),
+           batch_kv_len.data_ptr(), n_seqs, nq, nkv, page_size, n_pages, int(window), float(scale), part_o.data_ptr(),
+           part_ml.data_ptr(), counters.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin), _ptr(positions),
+           _ptr(slot_mapping), int(rotary_dim), 0 if cos_sin is None else cos_sin.shape[0], 1 if store else 0, float(eps),
+           float(weight_offset), stream_ptr())
 
 
 def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int, scale: float,
@@ -153,11 +186,10 @@ def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int,
     if not (FUSE_DECODE_QK and qkv.dtype == torch.bfloat16 and batch.n_prefill_seqs == 0 and batch.n_decode_seqs > 0
             and attention_mma.supports(head_dim, nq, nkv, batch.n_seqs)):
         return False
-    launch_fused = attention_mma.get(head_dim)[2]
-    vec = head_dim // 32
-    if launch_fused is None or (cos_sin is not None and (rotary_dim <= 0 or rotary_dim % (2 * vec))):
-        return False
     if qkv.stride(0) % 8 or qkv.data_ptr() % 16:
+        return False
+    vec = head_dim // 32
+    if head_dim % 32 or (cos_sin is not None and (rotary_dim <= 0 or rotary_dim % (2 * vec))):
         return False
     _need_cuda(out, qkv, kv_pages, q_weight, k_weight, cos_sin)
     _contig("kv_pages", kv_pages)
@@ -166,6 +198,14 @@ def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int,
     block_table = tables.block_tables
     assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
     n_seqs = batch.n_seqs
+    if USE_TMA_DECODE and attention_decode.supports(head_dim, nq, nkv, page_size, n_seqs):
+        _attention_decode_tma(out, None, qkv, kv_pages, block_table, batch.cu_q, batch.kv_len, n_seqs, nq, nkv, head_dim,
+                              scale, window, q_weight, k_weight, cos_sin, batch.positions, tables.slot_mapping, rotary_dim,
+                              eps, weight_offset, store)
+        return True
+    launch_fused = attention_mma.get(head_dim)[2]
+    if launch_fused is None:
+        return False
     tile = attention_mma.get(head_dim)[1]
     group = nq // nkv
     rows, head_blocks = min(group, 16), nkv * -(-group // 16)
@@ -214,6 +254,13 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
         if n_decode_seqs == 0:
             return
         n_prefill_tokens = n_prefill_seqs = 0
+    if n_decode_seqs > 0 and USE_TMA_DECODE and attention_decode.supports(head_dim, nq, nkv, page_size, n_seqs):
+        # single tokens: the kernel that streams the cache with TMA; what is left for the launch below are the
+        # prompt portions (if the tcgen05 kernel did not take them)
+        _attention_decode_tma(out, q, None, kv_pages, block_table, cu_q, kv_len, n_seqs, nq, nkv, head_dim, scale, window)
+        if n_prefill_tokens == 0:
+            return
+        n_decode_seqs = 0
     scratch_o = scratch_ml = counters = None
     max_pieces = blocks = 0
     if n_decode_seqs > 0:

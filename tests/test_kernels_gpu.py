@@ -350,33 +350,43 @@ def test_attention_mixed_batch(ops, kernel, dtype, nq, nkv, d, page, window):
     if kernel == "simt":
         ops.attention_simt(out, dev(q_all), dev(pages), dev(bt), dev(cu), kv, S, sum(news), nq, nkv, d, scale, window)
     else:
-        # "tensor_core": the mma.sync kernels alone; "tcgen05": prompt portions through the tcgen05 kernel
-        ops.USE_TCGEN05_ATTENTION = kernel == "tcgen05"
+        # "tensor_core": the mma.sync kernels alone; "tcgen05": prompt portions through the tcgen05 kernel and
+        # single tokens through the decode kernel that streams the cache with TMA
+        ops.USE_TCGEN05_ATTENTION = ops.USE_TMA_DECODE = kernel == "tcgen05"
         try:
             ops.attention_tensor_core(out, dev(q_all), dev(pages), dev(bt), dev(cu), kv, S,
                                       sum(n for n in news if n > 1), sum(1 for n in news if n > 1),
                                       sum(1 for n in news if n == 1), max(lens), nq, nkv, d, scale, window)
         finally:
-            ops.USE_TCGEN05_ATTENTION = True
+            ops.USE_TCGEN05_ATTENTION = ops.USE_TMA_DECODE = True
         if kernel == "tcgen05":
-            assert ops.attention_tcgen05_error(d) == 0, "a bounded wait of the tcgen05 kernel ran out"
+            assert ops.take_wait_errors() == [], "a bounded wait of a kernel ran out"
     ref = torch.cat(refs).reshape(-1, nq * d).float()
     t = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(out.cpu().float(), ref, **t)
 
 
-@pytest.mark.parametrize("nq,nkv,d,page,window,rot,norm", [(32, 8, 128, 256, 0, 128, True), (6, 2, 64, 16, 0, 64, True),
-                                                          (4, 4, 32, 8, 19, 16, True), (9, 3, 96, 5, 0, 96, False),
-                                                          (2, 1, 256, 64, 40, 0, True), (34, 1, 64, 16, 300, 32, True),
-                                                          (6, 2, 192, 16, 0, 192, True), (5, 1, 160, 8, 0, 80, True),
-                                                          (4, 2, 224, 16, 0, 0, False)])
-def test_attention_decode_from_the_projection_output(ops, nq, nkv, d, page, window, rot, norm):
+FUSED_SHAPES = [(32, 8, 128, 256, 0, 128, True), (6, 2, 64, 16, 0, 64, True), (4, 4, 32, 8, 19, 16, True),
+                (9, 3, 96, 5, 0, 96, False), (2, 1, 256, 64, 40, 0, True), (34, 1, 64, 16, 300, 32, True),
+                (6, 2, 192, 16, 0, 192, True), (5, 1, 160, 8, 0, 80, True), (4, 2, 224, 16, 0, 0, False)]
+# shapes that the decode kernel with TMA takes (head sizes in steps of 64, pages in steps of 64 keys): groups of
+# 1, 3, 5 and 34 heads (three head blocks), windows that end inside a tile, partial rotation, no norm
+TMA_FUSED_SHAPES = [(32, 8, 128, 256, 0, 128, True), (2, 1, 256, 64, 40, 0, True), (6, 2, 64, 64, 0, 64, True),
+                    (12, 4, 192, 64, 0, 96, True), (34, 1, 64, 128, 300, 32, True), (40, 8, 128, 64, 100, 128, False),
+                    (3, 3, 128, 192, 0, 64, True)]
+
+
+@pytest.mark.parametrize("tma,nq,nkv,d,page,window,rot,norm", [(False, *s) for s in FUSED_SHAPES] + [(True, *s) for s in TMA_FUSED_SHAPES])
+def test_attention_decode_from_the_projection_output(ops, tma, nq, nkv, d, page, window, rot, norm):
     """A step of single tokens: the decode kernel given qkv as the projection wrote it (it norms, rotates and
     stores by itself) against ``reference_attention`` over keys and values gathered from the cache, with the new
     query and key heads normed and rotated apart in float64 (the plain implementation's formulas); the cache
     afterwards holds the new keys and values and nothing else has changed; and again without storing, as a
     layer that reads another layer's cache runs."""
     from types import SimpleNamespace
+    from nanohybrid_vlm_b200.kernels import attention_decode
+    assert attention_decode.supports(d, nq, nkv, page) == tma or not tma
+    ops.USE_TMA_DECODE = tma
     rng = np.random.default_rng(11)
     g = torch.Generator().manual_seed(11)
     lens = [611, 1, 64, 65, 200, 7]                          # keys of each request, the new token included
@@ -385,6 +395,9 @@ def test_attention_decode_from_the_projection_output(ops, nq, nkv, d, page, wind
     pages = (torch.randn(n_pages, 2, nkv, page, d, generator=g) * 0.5).to(torch.bfloat16)   # stale contents everywhere
     free = list(rng.permutation(n_pages))
     tables = [[int(free.pop()) for _ in range(-(-L // page))] for L in lens]
+    for t, L in zip(tables, lens):                          # and NaN behind every request's last key, as in a fresh pool
+        if L % page:
+            pages[t[-1], :, :, L % page:] = float("nan")
     width = max(len(t) for t in tables)
     bt = torch.full((S, width), -1, dtype=torch.int32)
     for i, t in enumerate(tables):
@@ -450,11 +463,11 @@ def test_attention_decode_from_the_projection_output(ops, nq, nkv, d, page, wind
     torch.testing.assert_close(got.cpu().float(), want, rtol=2e-2, atol=2e-2)
     # the cache: the new keys and values where they belong (one step of bfloat16 apart at most: the kernel's
     # float32 arithmetic against float64), every other slot untouched
-    torch.testing.assert_close(pages_one.cpu().float(), pages_want.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(pages_one.cpu().float(), pages_want.float(), rtol=1e-2, atol=1e-2, equal_nan=True)
     untouched = torch.ones(n_pages, 2, nkv, page, dtype=torch.bool)
     for i, L in enumerate(lens):
         untouched[tables[i][(L - 1) // page], :, :, (L - 1) % page] = False
-    assert torch.equal(pages_one.cpu()[untouched], pages[untouched])
+    assert torch.equal(pages_one.cpu()[untouched].view(torch.int16), pages[untouched].view(torch.int16))
 
     # without storing: the new keys and values are in the cache already (the other run stored them)
     again = torch.full((S, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
@@ -462,7 +475,9 @@ def test_attention_decode_from_the_projection_output(ops, nq, nkv, d, page, wind
     assert ops.attention_decode_fused(again, dev(qkv), pages_two, views, batch, nq, nkv, d, scale, window,
                                       dev(qw) if norm else None, dev(kw) if norm else None, table, rot, 1e-6, 0.0, False)
     torch.testing.assert_close(again.cpu().float(), want, rtol=2e-2, atol=2e-2)
-    assert torch.equal(pages_two, before)
+    assert torch.equal(pages_two.view(torch.int16), before.view(torch.int16))
+    ops.USE_TMA_DECODE = True
+    assert ops.take_wait_errors() == []
 
 
 @pytest.mark.parametrize("vocab,rows", [(384, 5), (1000, 3), (151936, 4)])
@@ -494,3 +509,54 @@ def test_sampler_follows_the_distribution(ops):
     freq = torch.bincount(out.cpu().long(), minlength=7).double() / n
     p = torch.softmax(logits.double() / T, 0)
     assert (freq - p).abs().max() < 4 * math.sqrt(0.25 / n)
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 256, 0), (6, 2, 64, 64, 700), (16, 1, 128, 64, 0)])
+def test_attention_decode_many_requests_through_the_tma_ring(ops, nq, nkv, d, page, window):
+    """Forty single-token requests of 1 to 3,000 keys: every block of the persistent decode kernel walks many
+    tiles, whole requests and the ends of requests that it shares with its neighbours, and the ring is reused
+    many times over; against the float64 reference, with NaN wherever no key lies."""
+    from nanohybrid_vlm_b200.kernels import attention_decode
+    assert attention_decode.supports(d, nq, nkv, page)
+    rng = np.random.default_rng(5)
+    g = torch.Generator().manual_seed(5)
+    lens = [1, 2, 63, 64, 65, 3000, 2049] + rng.integers(1, 3000, 33).tolist()
+    S = len(lens)
+    n_pages = sum(-(-L // page) for L in lens) + 2
+    pages = torch.full((n_pages, 2, nkv, page, d), float("nan")).to(torch.bfloat16)
+    free = list(rng.permutation(n_pages))
+    scale = d ** -0.5
+    tables, qs, refs = [], [], []
+    for L in lens:
+        k = torch.randn(L, nkv, d, generator=g).to(torch.bfloat16)
+        v = torch.randn(L, nkv, d, generator=g).to(torch.bfloat16)
+        q = torch.randn(1, nq, d, generator=g).to(torch.bfloat16)
+        if L > 300:                                          # one far key stands out: losing it shows
+            far = L - window if window and L > window else 5
+            q[0] = 0
+            q[0, :, 1] = 6.0
+            k[far, :, 1] = 8.0
+            v[far] = 4.0
+        ids = [int(free.pop()) for _ in range(-(-L // page))]
+        kp = torch.full((len(ids) * page, nkv, d), float("nan")).to(torch.bfloat16)
+        vp = kp.clone()
+        kp[:L], vp[:L] = k, v
+        pages[ids, 0] = kp.view(len(ids), page, nkv, d).transpose(1, 2)
+        pages[ids, 1] = vp.view(len(ids), page, nkv, d).transpose(1, 2)
+        tables.append(ids)
+        qs.append(q)
+        refs.append(reference_attention(q, k, v, scale, window))
+    width = max(len(t) for t in tables)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    q_all = torch.cat(qs).reshape(S, nq * d)
+    out = torch.full_like(q_all, float("nan"), device="cuda")
+    cu = torch.arange(S + 1, dtype=torch.int32)
+    for repeat in range(2):                                  # the scratch and the counters are left ready for the next launch
+        out.fill_(float("nan"))
+        ops.attention_tensor_core(out, dev(q_all), dev(pages), dev(bt), dev(cu), dev(torch.tensor(lens, dtype=torch.int32)), S,
+                                  0, 0, S, max(lens), nq, nkv, d, scale, window)
+        ref = torch.cat(refs).reshape(S, nq * d).float()
+        torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+    assert ops.take_wait_errors() == []
