@@ -1,18 +1,18 @@
 // bfloat16 attention of single decoded tokens over cache pages, for head sizes in steps of 64 and pages that are a
-// multiple of 64 keys; compiled once per head size (-DNHV_ATTN_D=<head size>).  Replaces the library call at
+// multiple of 32 keys; compiled once per head size (-DNHV_ATTN_D=<head size>).  Replaces the library call at
 // nanovllm/layers/attention.py:72-74 (flash_attn_with_kvcache).
 //
 // Decoding reads every key and value of every live request once and computes almost nothing, so the kernel is built
 // around keeping HBM busy:
 //
-//  * Persistent, one block per SM.  The work is the flat list of 64-key tiles of every (request with one new token,
+//  * Persistent, one block per SM.  The work is the flat list of 32-key tiles of every (request with one new token,
 //    block of up to 16 query heads of one KV head), request-major; block c owns the contiguous tiles
 //    [c * T / NB, (c + 1) * T / NB), so every SM reads the same number of bytes whatever the batch looks like.
 //  * A producer warp streams its block's tiles through a ring of shared-memory stages with TMA tile copies straight
 //    from the paged pool (the pool seen as one matrix [pages * 2 * kv_heads * page_size, D]; boxes of 64 columns x
-//    64 keys in the 128-byte swizzle; plain per-block copies, no multicast; completion counted in bytes on an
+//    32 keys in the 128-byte swizzle; plain per-block copies, no multicast; completion counted in bytes on an
 //    mbarrier).  It looks the pages of 32 tiles up at a time and runs ahead of the consumers across the borders of
-//    requests, so the ring never drains: up to STAGES * 2 * 64 * D * 2 bytes are in flight per SM.
+//    requests, so the ring never drains: up to STAGES * 2 * 32 * D * 2 bytes are in flight per SM.
 //  * The consumer warps (four for head sizes up to 128) take whole tiles in turn (tile t of the block goes to warp
 //    t % NCW): no warp waits for another while a piece lasts.  mma.sync.m16n8k16 bf16 with fp32 accumulation, online softmax in fp32 on base-2
 //    exponents, the rows being the query heads of the group (padded to 16).  At the end of a piece (a block's tiles
@@ -51,7 +51,7 @@ constexpr int D = NHV_ATTN_D;
 static_assert(D % 64 == 0 && D >= 64 && D <= 256, "head sizes 64, 128, 192 and 256");
 constexpr int CH = D / 8;          // 16-byte chunks in a row
 constexpr int DB = D / 64;         // 128-byte column blocks of a head (one TMA box each)
-constexpr int BN = 64;             // keys per tile
+constexpr int BN = 32;             // keys per tile
 constexpr int KS = D / 16;         // k-steps of Q.K^T
 constexpr int DN = D / 8;          // n-tiles of P.V
 constexpr int TILE_BYTES = BN * D * 2;                 // one K tile or one V tile
@@ -59,9 +59,9 @@ constexpr int STAGE_BYTES = 2 * TILE_BYTES;
 // Consumer warps and ring stages.  A stage is always consumed by the same warp (STAGES is a multiple of NCW and
 // tile number t of the block goes to warp t % NCW and stage t % STAGES): a warp's waits on one barrier then follow
 // one another, so it can never ask for a phase while the one before it is still filling (a wait by parity cannot
-// tell those two apart).
+// tell those two apart).  Every warp has two stages, so its next tile is on its way while it works on one.
 constexpr int NCW = D <= 128 ? 4 : (D == 192 ? 3 : 2);
-constexpr int STAGES = D == 64 ? 8 : NCW;
+constexpr int STAGES = 2 * NCW;
 static_assert(STAGES % NCW == 0, "every stage must belong to one consumer warp");
 constexpr int THREADS = (NCW + 1) * 32;
 constexpr int Q_BYTES = 16 * D * 2;
@@ -69,7 +69,7 @@ constexpr int MERGE_BYTES = NCW * 16 * D * 4 + NCW * 16 * 2 * 4;
 constexpr int MAX_SEQS = 512;
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + MERGE_BYTES + Q_BYTES;
 static_assert(SMEM_BYTES + 8 * 1024 <= 227 * 1024, "ring, merge buffer and queries must fit one block's shared memory");
-constexpr int MIN_TILES = 2;
+constexpr int MIN_TILES = 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
 typedef __nv_bfloat16 bf16;
@@ -156,7 +156,7 @@ struct RowState {
   float o[DN][4];
 };
 
-// One warp, 16 rows, 32 keys of a tile starting at tile row `kb`: scores, mask, online softmax, P.V.
+// One warp, 16 rows, the 32 keys of a tile starting at tile row `kb`: scores, mask, online softmax, P.V.
 // key_base: absolute index of tile row 0.  Row i (0/1) of this thread sees keys in [lo, row_hi[i]].
 __device__ __forceinline__ void warp_half_tile(RowState& st, const uint32_t (&qf)[KS][4], const bf16* ks, const bf16* vs,
                                                int kb, int key_base, int lo, const int (&row_hi)[2], float scale_log2) {
@@ -494,7 +494,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       // value rows of keys outside [lo, total) are cleared: their weight is zero, but zero times what lies there
       // (stale numbers, NaN of a fresh pool) must be zero too
       const int r_lo = there ? min(BN, max(0, lo - key_base)) : BN;            // rows [0, r_lo) are before the range
-      const int r_hi = there ? min(BN, max(0, total - key_base)) : BN;         // rows [r_hi, 64) are beyond it
+      const int r_hi = there ? min(BN, max(0, total - key_base)) : BN;         // rows [r_hi, BN) are beyond it
       if (r_lo > 0 || r_hi < BN) {
         for (int id = lane; id < BN * CH; id += 32) {
           const int r = id / CH, cc = id - r * CH;
@@ -504,10 +504,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       }
       if (wrote) __syncwarp();
       const int lo_t = there ? lo : 0x7fffffff;               // a tile whose page is missing: no key counts
-#pragma unroll
-      for (int kb = 0; kb < BN; kb += 32)
-        if (key_base + kb < total && key_base + kb + 32 > lo_t)
-          warp_half_tile(st, qf, kt, vt, kb, key_base, lo_t, row_hi, p.scale_log2);
+      if (key_base < total && key_base + BN > lo_t)
+        warp_half_tile(st, qf, kt, vt, 0, key_base, lo_t, row_hi, p.scale_log2);
       if (wrote) fence_async_smem();                          // this warp's stores before the next copy into the stage
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[stage]);
@@ -521,12 +519,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       l += __shfl_xor_sync(0xffffffffu, l, 1);
       l += __shfl_xor_sync(0xffffffffu, l, 2);
       const int R = (lane >> 2) + 8 * i;
+      if (R >= gn) continue;                                   // rows beyond the group hold nothing
       float* dst = mo + ((size_t)warp * 16 + R) * D + ((lane & 3) << 1);
 #pragma unroll
-      for (int n = 0; n < DN; ++n) {
-        dst[n * 8] = st.o[n][2 * i];
-        dst[n * 8 + 1] = st.o[n][2 * i + 1];
-      }
+      for (int n = 0; n < DN; ++n)
+        *reinterpret_cast<float2*>(dst + n * 8) = make_float2(st.o[n][2 * i], st.o[n][2 * i + 1]);
       if ((lane & 3) == 0) {
         mml[(warp * 16 + R) * 2] = st.m[i];
         mml[(warp * 16 + R) * 2 + 1] = l;
