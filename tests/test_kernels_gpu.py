@@ -560,3 +560,37 @@ def test_attention_decode_many_requests_through_the_tma_ring(ops, nq, nkv, d, pa
         ref = torch.cat(refs).reshape(S, nq * d).float()
         torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
     assert ops.take_wait_errors() == []
+
+
+def test_attention_of_more_requests_than_the_tensor_core_kernels_plan_for(ops):
+    """600 single-token requests in one step: beyond the 512 that the tensor-core decode kernels plan for, so
+    ``ops.attention`` runs the step on the CUDA-core kernel instead of refusing it in the middle of generation."""
+    from types import SimpleNamespace
+    from nanohybrid_vlm_b200.kernels import attention_mma
+    nq, nkv, d, page, S = 4, 2, 16, 4, 600
+    assert S > attention_mma.MAX_SEQS
+    g = torch.Generator().manual_seed(2)
+    rng = np.random.default_rng(2)
+    lens = rng.integers(1, 20, S).tolist()
+    per = [-(-L // page) for L in lens]
+    n_pages = sum(per)
+    pages = torch.full((n_pages, 2, nkv, page, d), float("nan")).to(torch.bfloat16)
+    order = rng.permutation(n_pages).tolist()
+    bt = torch.full((S, max(per)), -1, dtype=torch.int32)
+    qs, refs = [], []
+    for i, L in enumerate(lens):
+        ids = [order.pop() for _ in range(per[i])]
+        bt[i, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
+        k = torch.randn(L, nkv, d, generator=g).to(torch.bfloat16)
+        v = torch.randn(L, nkv, d, generator=g).to(torch.bfloat16)
+        q = torch.randn(1, nq, d, generator=g).to(torch.bfloat16)
+        for j in range(L):
+            pages[ids[j // page], 0, :, j % page], pages[ids[j // page], 1, :, j % page] = k[j], v[j]
+        qs.append(q)
+        refs.append(reference_attention(q, k, v, d ** -0.5, 0))
+    q_all = torch.cat(qs).reshape(S, nq * d)
+    out = torch.full_like(q_all, float("nan"), device="cuda")
+    batch = SimpleNamespace(n_seqs=S, n_tokens=S, n_prefill_seqs=0, n_prefill_tokens=0, n_decode_seqs=S, max_kv_len=max(lens),
+                            cu_q=dev(torch.arange(S + 1, dtype=torch.int32)), kv_len=dev(torch.tensor(lens, dtype=torch.int32)))
+    ops.attention(out, dev(q_all), dev(pages), SimpleNamespace(block_tables=dev(bt)), batch, nq, nkv, d, d ** -0.5)
+    torch.testing.assert_close(out.cpu().float(), torch.cat(refs).reshape(S, nq * d).float(), rtol=2e-2, atol=2e-2)
