@@ -214,9 +214,7 @@ def bench_ours(args) -> dict:
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         h2d, d2h = (llm.h2d_bytes - h0) / steps, (llm.d2h_bytes - d0) / steps
-        for seq in list(llm.scheduler.running):
-            llm.scheduler.cache.free(seq.seq_id)
-        llm.scheduler.running.clear()
+        llm.abort_all()
         return n_tok / dt, h2d, d2h
 
     if args.only == "decode":

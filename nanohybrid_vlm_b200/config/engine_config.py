@@ -4,8 +4,8 @@ The reference keeps them in one dataclass (nanovllm/config.py:9-152) that the en
 point fills from keyword arguments (nanovllm/engine/llm_engine.py:179-181).  The
 options that belong to its hybrid (GDN, vision, joint prefix cache) path are absent.
 Options that the reference does not have: ``dtype`` (run the checkpoint in another
-precision; ``"float32"`` is the true 32-bit path), ``seed``, ``decode_weight_copy`` and
-``poison_cache``.
+precision; ``"float32"`` is the true 32-bit path), ``seed``, ``decode_weight_copy``,
+``async_decode`` and ``poison_cache``.
 """
 from __future__ import annotations
 
@@ -36,6 +36,9 @@ class Config:
     decode_weight_copy: bool | None = None   # a second copy of the matrices a decode step streams, one share per SM (faster
                                              # small batches, twice the weight memory); None: when it fits in a
                                              # quarter of the free device memory
+    async_decode: bool = True                # launch a decode step before the host has read the tokens of the one before
+                                             # (they are passed on on the device); an end-of-sequence token is then seen
+                                             # one step late and the extra token dropped.  Needs the CUDA graphs.
     poison_cache: bool = False               # fill the cache pools with NaN at start: a read of a slot that no step
                                              # wrote shows in the logits (tests, replay)
     dtype: str | torch.dtype | None = None   # None: the checkpoint's own

@@ -108,6 +108,12 @@ class BatchBuilder:
         self._layouts[key] = (sections, off)
         return sections, off
 
+    def token_ids_on_device(self, bucket: int, table_width: int) -> torch.Tensor:
+        """Where a padded step of ``bucket`` single tokens keeps its token ids on the device."""
+        sec, _ = self._layout(bucket, bucket, bucket, table_width)
+        o, n = sec["token_ids"]
+        return self._dev[o:o + n]
+
     def build(self, items: list[StepItem], table_width: int | None = None, sampling=None,
               pad_to: int | None = None, views: bool = True) -> StepBatch | None:
         """``sampling``: one (temperature, seed, position of the token being chosen) per wanted row.

@@ -17,7 +17,7 @@ from ..sampling.params import SamplingParams
 from .batch import StepItem
 from .runner import ModelRunner
 from .scheduler import Scheduler
-from .sequence import Sequence
+from .sequence import PENDING, Sequence
 
 
 @dataclass(slots=True)
@@ -101,6 +101,9 @@ class LLMEngine:
         self.d2h_bytes = 0
         self.last_sampled_ids: list[int] = []   # requests of the last step that chose a token, in the order of the
                                                 # rows of ``model_runner.last_logits``
+        # a launched decode step whose tokens the host has not read yet: (requests, their places, handle, time)
+        self._inflight = None
+        self.async_decode = bool(config.async_decode) and not config.enforce_eager
 
     @staticmethod
     def _load_tokenizer(model_dir: str):
@@ -132,15 +135,67 @@ class LLMEngine:
         return seq.seq_id
 
     def is_finished(self) -> bool:
-        return self.scheduler.is_finished()
+        return self.scheduler.is_finished() and self._inflight is None
 
     # ------------------------------------------------------------------ one step
     def step(self):
-        """Schedule, run one mixed batch, sample, book.  Returns (finished [(seq_id, token_ids)], StepStats)."""
+        """Schedule, run one mixed batch, sample, book.  Returns (finished [(seq_id, token_ids)], StepStats).
+
+        A step of decoded tokens only is launched without waiting for it (``async_decode``): the call returns what
+        the step BEFORE it finished, and the tokens pass from one step to the next on the device.  Any other step
+        (prompt portions, a change in the set of decoding requests) first waits for the step in flight."""
         t0 = perf_counter()
-        plan = self.scheduler.schedule()
+        outputs = []
+        if self.scheduler.is_finished():
+            if self._inflight is None:
+                raise RuntimeError("nothing to do: no request is waiting, running or in flight")
+            self.last_sampled_ids = []
+            return self._drain(), StepStats(0, 0, perf_counter() - t0)
+        try:
+            plan = self.scheduler.schedule()
+        except RuntimeError:
+            # nothing fits: the step in flight may hold what is missing (requests at their length give their pages
+            # back when their last token has been read)
+            if self._inflight is None:
+                raise
+            outputs += self._drain()
+            if self.scheduler.is_finished():
+                self.last_sampled_ids = []
+                return outputs, StepStats(0, 0, perf_counter() - t0)
+            plan = self.scheduler.schedule()
+        runner = self.model_runner
+        pure_decode = all(s.num_scheduled_tokens == 1 and s.num_cached_tokens + 1 == len(s) for s in plan.seqs)
+        items = None
+        if self.async_decode and pure_decode:
+            fed = self._inflight is not None and [s.seq_id for s in self._inflight[0]] == [s.seq_id for s in plan.seqs]
+            if self._inflight is not None and not fed:
+                outputs += self._drain()                     # other requests than the step in flight: read it first
+            seqs = [s for s in plan.seqs if not s.is_finished]
+            if seqs:
+                items = [StepItem(s.seq_id, [0 if s.token_ids[-1] == PENDING else s.token_ids[-1]], s.num_cached_tokens, [0])
+                         for s in seqs]
+                if not runner.can_launch(items):
+                    items = None
+            if items is not None:
+                for s in seqs:
+                    m = self.request_metrics[s.seq_id]
+                    if m.first_scheduled_time is None:
+                        m.first_scheduled_time = t0
+                self.last_sampled_ids = [s.seq_id for s in seqs]
+                handle = runner.launch(items, [(s.temperature, s.seed, len(s)) for s in seqs],
+                                       feed_from=self._inflight[2] if fed and len(seqs) == len(plan.seqs) else None)
+                self.h2d_bytes += runner.builder.bytes_last_copy
+                self.d2h_bytes += 4 * (len(seqs) + 1)
+                places = self.scheduler.advance(seqs)
+                previous, self._inflight = self._inflight if fed else None, (seqs, places, handle)
+                if previous is not None:
+                    outputs += self._resolve(previous)
+                return outputs, StepStats(len(seqs), 0, perf_counter() - t0)
+        # ---- the step is run and read at once
+        outputs += self._drain()
+        seqs = [s for s in plan.seqs if not s.is_finished]    # the step just read may have ended some of them
         items, sampled = [], []
-        for seq in plan.seqs:
+        for seq in seqs:
             start, n = seq.num_cached_tokens, seq.num_scheduled_tokens
             last = start + n == len(seq)
             items.append(StepItem(seq.seq_id, seq.token_ids[start:start + n], start, [n - 1] if last else []))
@@ -149,7 +204,8 @@ class LLMEngine:
             m = self.request_metrics[seq.seq_id]
             if m.first_scheduled_time is None:
                 m.first_scheduled_time = t0
-        runner = self.model_runner
+        if not items:
+            return outputs, StepStats(0, 0, perf_counter() - t0)
         tokens = {}
         self.last_sampled_ids = [s.seq_id for s in sampled]
         if sampled:
@@ -159,18 +215,42 @@ class LLMEngine:
         else:
             runner.step(items)
         self.h2d_bytes += runner.builder.bytes_last_copy
-        self.scheduler.postprocess(plan.seqs, [tokens.get(s.seq_id) for s in plan.seqs])
-        now = perf_counter()
+        self.scheduler.postprocess(seqs, [tokens.get(s.seq_id) for s in seqs])
+        outputs += self._book(sampled, perf_counter())
+        n_decode = sum(1 for s in seqs if s in sampled and len(items[seqs.index(s)].tokens) == 1)
+        return outputs, StepStats(plan.num_decode_tokens if len(seqs) == len(plan.seqs) else n_decode,
+                                  plan.num_prefill_tokens, perf_counter() - t0)
+
+    def _book(self, sampled: list[Sequence], now: float) -> list:
         outputs = []
         for seq in sampled:
             m = self.request_metrics[seq.seq_id]
             m.num_completion_tokens = seq.num_completion_tokens
             if m.first_token_time is None:
                 m.first_token_time = now
-            if seq.is_finished:
+            if seq.is_finished and m.finish_time is None:
                 m.finish_time = now
                 outputs.append((seq.seq_id, seq.completion_token_ids))
-        return outputs, StepStats(plan.num_decode_tokens, plan.num_prefill_tokens, now - t0)
+        return outputs
+
+    def _resolve(self, flight) -> list:
+        """Read the tokens of a launched step and book them."""
+        seqs, places, handle = flight
+        self.scheduler.resolve(seqs, places, handle.read())
+        return self._book(seqs, perf_counter())
+
+    def abort_all(self) -> None:
+        """Drop every request (waiting, running or in flight) and give back what they hold."""
+        self._drain()
+        for seq in list(self.scheduler.running) + list(self.scheduler.waiting):
+            self.scheduler._finish(seq)
+
+    def _drain(self) -> list:
+        """Wait for the step in flight, if there is one."""
+        if self._inflight is None:
+            return []
+        flight, self._inflight = self._inflight, None
+        return self._resolve(flight)
 
     def get_completed_request_metrics(self) -> list[RequestMetrics]:
         return sorted((m for m in self.request_metrics.values() if m.finish_time is not None), key=lambda m: m.seq_id)

@@ -18,6 +18,21 @@ from .batch import BatchBuilder, StepItem
 from .model import CausalLM
 
 
+class InFlight:
+    """A launched decode step: its chosen tokens are on the device (``device_tokens``, overwritten by the next
+    replay of the same bucket) and on their way to pinned host memory."""
+
+    def __init__(self, runner, n: int, bucket: int, device_tokens: torch.Tensor, slot):
+        self.runner, self.n, self.bucket, self.device_tokens, self._slot = runner, n, bucket, device_tokens, slot
+
+    def read(self) -> list[int]:
+        """Wait for the step and return its tokens (raises ``KernelError`` if a bounded wait of a kernel ran out)."""
+        buf, event = self._slot
+        event.synchronize()
+        host = buf[:self.bucket + 1].tolist()
+        return ModelRunner._checked(host[:self.n] + host[-1:])
+
+
 class ModelRunner:
     def __init__(self, config: Config, *, random_weights_seed: int | None = None, device: str = "cuda:0"):
         if not torch.cuda.is_available():
@@ -64,6 +79,9 @@ class ModelRunner:
         self._graphs: dict[int, tuple] = {}
         self._graph_pool = None
         self.last_logits: torch.Tensor | None = None    # fp32 logits of the last ``run`` (valid until the next one)
+        widest = (self.graph_buckets[-1] if self.graph_buckets else 0) + 1
+        self._host_tokens = [(torch.empty(widest, dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(2)]
+        self._host_turn = 0
 
     def _prepare_decode_weights(self) -> int:
         """Second copies of the matrices that a decode step streams, laid out for the weight-streaming kernel
@@ -153,6 +171,40 @@ class ModelRunner:
         """For callers of ``step`` (logits, no sampler): raise ``KernelError`` if a bounded wait of a kernel ran
         out since the last check.  Synchronises the device."""
         ops.raise_wait_errors()
+
+    # ------------------------------------------------------------------ a decode step whose tokens are read later
+    def can_launch(self, items: list[StepItem]) -> bool:
+        """True if ``launch`` takes these items: single tokens that all want their logits, within a graph bucket."""
+        return self._bucket(items) is not None
+
+    @torch.no_grad()
+    def launch(self, items: list[StepItem], sampling, feed_from: "InFlight | None" = None) -> "InFlight":
+        """Start a step of single tokens (the captured graph of its bucket) and return at once; ``InFlight.read()``
+        gives its tokens later.  ``feed_from``: the step before it, still in flight, over the same requests in the
+        same order: every item's token is then taken on the device from that step's chosen tokens (the items' own
+        token values are place-holders), so the host need not have read them."""
+        bucket = self._bucket(items)
+        if bucket is None:
+            raise ValueError("launch takes single tokens that all want their logits, within a graph bucket")
+        if bucket not in self._graphs:
+            self._capture(bucket)
+        graph, tokens, launches, logits = self._graphs[bucket]
+        n = len(items)
+        self.builder.build(items, table_width=self.max_pages_per_seq, sampling=sampling, pad_to=bucket, views=False)
+        if feed_from is not None:
+            if feed_from.n != n or feed_from.bucket != bucket:
+                raise ValueError("a step can only be fed by a step over the same requests")
+            # the tokens that the step before chose, straight into this step's token ids (after the host's copy of
+            # the batch arrays, before the graph that reads them)
+            self.builder.token_ids_on_device(bucket, self.max_pages_per_seq)[:n].copy_(feed_from.device_tokens[:n])
+        graph.replay()
+        library.LAUNCHES += launches
+        self.last_logits = logits[:n]
+        slot = self._host_tokens[self._host_turn]
+        self._host_turn ^= 1
+        slot[0][:bucket + 1].copy_(tokens, non_blocking=True)     # tokens and health word, before the next replay overwrites them
+        slot[1].record()
+        return InFlight(self, n, bucket, tokens, slot)
 
     def _bucket(self, items) -> int | None:
         if not self.graph_buckets or len(items) > self.graph_buckets[-1]:

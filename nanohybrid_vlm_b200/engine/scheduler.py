@@ -29,7 +29,7 @@ from collections import deque
 from dataclasses import dataclass, field
 
 from ..cache import CacheManager
-from .sequence import Sequence, SequenceStatus
+from .sequence import PENDING, Sequence, SequenceStatus
 
 
 @dataclass
@@ -153,6 +153,51 @@ class Scheduler:
         self.running.remove(seq)
         self.waiting.append(seq)
         plan.preempted_seq_ids.append(seq.seq_id)
+
+    # ------------------------------------------------------------------ a step whose tokens are read later
+    def advance(self, seqs: list[Sequence]) -> list[int]:
+        """Book a launched step of single tokens whose chosen tokens are still on the device: every request gets a
+        place for its token (``PENDING``) so that the next step can be planned, and a request that has reached its
+        length leaves ``running`` (its cache is kept until ``resolve`` sees its last token).  Returns, per request,
+        the index of the place in its token list."""
+        places = []
+        for seq in seqs:
+            seq.num_cached_tokens += seq.num_scheduled_tokens
+            seq.num_scheduled_tokens = 0
+            places.append(len(seq))
+            seq.append_token(PENDING)
+            if seq.num_completion_tokens >= seq.max_tokens or len(seq) >= self.max_model_len:
+                seq.finishing = True
+                self.running.remove(seq)
+            elif self.cache.has_windows:
+                self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
+        return places
+
+    def resolve(self, seqs: list[Sequence], places: list[int], token_ids: list[int]) -> None:
+        """The tokens of a step booked with ``advance`` have arrived: they take their places; a request stops at
+        the end-of-sequence token (whatever a later step, launched meanwhile, computed for it is dropped) or at
+        its length."""
+        for seq, place, token in zip(seqs, places, token_ids):
+            if seq.is_finished or place >= len(seq):
+                continue                                      # it ended at an earlier token while this step ran
+            seq.token_ids[place] = token
+            if self.cache.prefix_cache and seq.seq_id in self.cache:
+                known = min(seq.num_cached_tokens, place + 1)
+                self.cache.commit(seq.seq_id, seq.token_ids, known)
+            stop = not seq.ignore_eos and token == self.eos
+            if stop or (seq.finishing and place == len(seq) - 1):
+                del seq.token_ids[place + 1:]
+                self._finish(seq)
+
+    def _finish(self, seq: Sequence) -> None:
+        seq.status = SequenceStatus.FINISHED
+        seq.finishing = False
+        if seq.seq_id in self.cache:
+            self.cache.free(seq.seq_id)
+        if seq in self.running:
+            self.running.remove(seq)
+        if seq in self.waiting:
+            self.waiting.remove(seq)
 
     # ------------------------------------------------------------------ after the step
     def postprocess(self, seqs: list[Sequence], token_ids: list[int | None]) -> None:

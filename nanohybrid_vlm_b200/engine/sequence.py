@@ -13,6 +13,9 @@ class SequenceStatus(Enum):
     FINISHED = auto()
 
 
+PENDING = -1        # stands in a token list for a token that the GPU has chosen but the host has not read yet
+
+
 class Sequence:
     counter = count()
 
@@ -28,6 +31,7 @@ class Sequence:
         self.ignore_eos = sampling_params.ignore_eos
         self.seed = sampling_params.seed if sampling_params.seed is not None else (seed if seed is not None else self.seq_id)
         self.num_preemptions = 0
+        self.finishing = False              # no further token is wanted (length), the last one is still on its way
 
     def __len__(self) -> int:
         return len(self.token_ids)

@@ -172,3 +172,37 @@ def test_prefill_first_with_a_pool_smaller_than_the_work(model_dirs, plain_model
     assert [o["token_ids"] for o in llm.generate(prompts, sp, use_tqdm=False)] == want
     llm.model_runner.cache.check()
     assert all(p.num_free == p.num_pages for p in llm.model_runner.cache.pools)
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_decode_steps_launched_ahead_give_the_same_tokens(name, model_dirs, plain_models):
+    """``async_decode``: a decode step is launched before the tokens of the one before have been read.  Greedy and
+    seeded sampling give the same tokens as with every step read at once, also when requests end at different
+    lengths, when one meets its end-of-sequence token in the middle, and when pages run out (preemption)."""
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompts = prompts_for(name, (5, 17, 33, 2), seed=21)
+    ref = [plain_models[name].greedy(p, 14) for p in prompts]
+    eos = ref[1][6]                                           # request 1 stops at its 7th token (or earlier, if it repeats)
+    sps = [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=i != 1) for i, n in enumerate((14, 14, 9, 3))]
+    want = [r[:sp.max_tokens] for r, sp in zip(ref, sps)]
+    want[1] = ref[1][:ref[1].index(eos) + 1]
+    for async_decode in (True, False):
+        llm = make_llm(model_dirs[name], name, eos=eos, async_decode=async_decode)
+        assert llm.async_decode == async_decode
+        out = llm.generate(prompts, sps, use_tqdm=False)
+        assert [o["token_ids"] for o in out] == want, f"async_decode={async_decode}"
+        llm.model_runner.cache.check()
+        assert all(p.num_free == p.num_pages for p in llm.model_runner.cache.pools)
+        done = {m.seq_id: m.num_completion_tokens for m in llm.get_completed_request_metrics()}
+        assert sorted(done.values()) == sorted(len(w) for w in want)
+        del llm
+    # temperature sampling with seeds, and a pool so small that decoding requests are preempted
+    sps = [SamplingParams(temperature=0.8, max_tokens=12, ignore_eos=True, seed=50 + i) for i in range(4)]
+    outs = []
+    for async_decode in (True, False):
+        page = 16 if name == "A" else 8
+        llm = make_llm(model_dirs[name], name, async_decode=async_decode, num_kvcache_blocks=-(-sum(len(p) for p in prompts) // page) + 5)
+        outs.append([o["token_ids"] for o in llm.generate(prompts, sps, use_tqdm=False)])
+        assert llm.scheduler.num_preemptions > 0
+        del llm
+    assert outs[0] == outs[1]

@@ -82,8 +82,9 @@ def test_the_sampler_hands_the_error_word_to_the_host_and_the_runner_raises(star
 
 @pytest.mark.parametrize("eager", [True, False])
 def test_generation_stops_with_the_kernels_name(starved, eager, model_dirs):
-    """Through the entry point, eagerly and through a captured decode graph: the step after a wait ran out
-    raises instead of handing out tokens."""
+    """Through the entry point, eagerly and through a captured decode graph: the step that reads the tokens of
+    the step in which a wait ran out raises instead of handing them out (with decode steps launched ahead of the
+    read that is the call after next)."""
     from nanohybrid_vlm_b200 import LLM, SamplingParams
     from nanohybrid_vlm_b200.kernels import KernelError
     llm = LLM(model_dirs["A"], dtype="bfloat16", kvcache_block_size=16, num_kvcache_blocks=32, max_num_seqs=4,
@@ -94,7 +95,11 @@ def test_generation_stops_with_the_kernels_name(starved, eager, model_dirs):
     run_product(starved, starve=True)
     with pytest.raises(KernelError, match="a bounded wait ran out in gemm_slab"):
         llm.step()
-    llm.step()                                            # the word was taken: the engine goes on
+        llm.step()
+    llm.abort_all()                                       # the requests of a failed step are given up
+    llm.add_request([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    while not llm.is_finished():                          # the word was taken: the engine goes on
+        llm.step()
 
 
 def test_replay_checks_every_step(starved, model_dirs):
