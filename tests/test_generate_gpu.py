@@ -198,10 +198,11 @@ def test_decode_steps_launched_ahead_give_the_same_tokens(name, model_dirs, plai
         del llm
     # temperature sampling with seeds, and a pool so small that decoding requests are preempted
     sps = [SamplingParams(temperature=0.8, max_tokens=12, ignore_eos=True, seed=50 + i) for i in range(4)]
+    prompts = prompts_for(name, (15, 16, 31, 8), seed=22)        # every one of them needs another page on the way
     outs = []
     for async_decode in (True, False):
         page = 16 if name == "A" else 8
-        llm = make_llm(model_dirs[name], name, async_decode=async_decode, num_kvcache_blocks=-(-sum(len(p) for p in prompts) // page) + 5)
+        llm = make_llm(model_dirs[name], name, async_decode=async_decode, num_kvcache_blocks=sum(-(-len(p) // page) for p in prompts))
         outs.append([o["token_ids"] for o in llm.generate(prompts, sps, use_tqdm=False)])
         assert llm.scheduler.num_preemptions > 0
         del llm
