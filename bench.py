@@ -9,7 +9,8 @@ The default run has the layer sizes of the Qwen3-8B-shaped configuration (36 lay
 2,048-token uniform-random prompts, decoding inside a 4,096-token context.  A "step" is one decode
 step of the whole batch.  It prints ONE JSON line:
 
-* ``value``: decoded tokens per second, K steps timed on the device with CUDA events;
+* ``value``: decoded tokens per second, K steps of the model runner timed on the device with CUDA events (a step is
+  launched before the host has read the tokens of the step before it, as generation does it);
 * ``e2e``: the same through the Python entry point (``LLM.add_request`` / ``LLM.step``): host
   token lists in, chosen tokens back on the host every step;
 * ``prefill``: one 2,048-token prompt in one step; ``frac`` = its flops / time / bf16 peak;
@@ -151,7 +152,7 @@ def bench_ours(args) -> dict:
         pages = max_b * (CONTEXT // PAGE) + 2 * (CONTEXT // PAGE)
         llm = LLM(d, random_weights_seed=SEED, kvcache_block_size=PAGE, num_kvcache_blocks=pages,
                   max_model_len=CONTEXT, max_num_seqs=max_b, max_num_batched_tokens=8192, seed=SEED,
-                  enforce_eager=args.eager)
+                  enforce_eager=args.eager, async_decode=not args.sync)
     runner = llm.model_runner
     params = SamplingParams(temperature=0.0, max_tokens=CONTEXT - PROMPT_LEN, ignore_eos=True)
 
@@ -168,12 +169,22 @@ def bench_ours(args) -> dict:
             lens[i] = PROMPT_LEN
         last = {i: 1 for i in ids}
 
+        flight = [None]
+
         def one():
+            """One decode step as generation runs it: launched before the tokens of the step before it have been
+            read (they pass on the device), then that step's tokens are read; with --sync, or eagerly, run and read."""
             items = []
             for i in ids:
                 runner.cache.allocate(i, lens[i] + 1)
                 items.append(StepItem(i, [last[i]], lens[i], [0]))
-            chosen = runner.run(items, [(0.0, n, lens[i] + 1) for n, i in enumerate(ids)])
+            sampling = [(0.0, n, lens[i] + 1) for n, i in enumerate(ids)]
+            if args.sync or not runner.can_launch(items):
+                chosen = runner.run(items, sampling)
+            else:
+                handle = runner.launch(items, sampling, feed_from=flight[0])
+                chosen = flight[0].read() if flight[0] is not None else [last[i] for i in ids]
+                flight[0] = handle
             for i, t in zip(ids, chosen):
                 last[i] = t
                 lens[i] += 1
@@ -192,6 +203,8 @@ def bench_ours(args) -> dict:
         ms = e0.elapsed_time(e1) / steps
         launches = klib.LAUNCHES
         ctx_mid = ctx0 + steps / 2
+        if flight[0] is not None:
+            flight[0].read()
         for i in ids:
             runner.cache.free(i)
         return ms, launches, ctx_mid
@@ -320,7 +333,8 @@ def bench_workload(args) -> dict:
         with open(os.path.join(d, "config.json"), "w") as f:
             json.dump(cfg, f)
         llm = LLM(d, random_weights_seed=seed, kvcache_block_size=PAGE, max_model_len=context, max_num_seqs=max_seqs,
-                  max_num_batched_tokens=16384, seed=seed, enforce_eager=args.eager, enable_prefix_cache=False)
+                  max_num_batched_tokens=16384, seed=seed, enforce_eager=args.eager, enable_prefix_cache=False,
+                  async_decode=not args.sync)
     params = SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True)
     # warm-up: one short request through prefill and the decode graph of the smallest bucket
     llm.generate([prompts[0][:64]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True), use_tqdm=False)
@@ -639,6 +653,7 @@ def main() -> int:
                     help="fewer layers than the full model (sizes of a layer unchanged); recorded in config")
     ap.add_argument("--workload", default="8b", choices=["8b", "0.6b", "32b"],
                     help="8b: the headline line; 0.6b / 32b: the baseline's other workloads through LLM.add_request / step")
+    ap.add_argument("--sync", action="store_true", help="read every decode step's tokens before the next is launched (async_decode off)")
     ap.add_argument("--requests", type=int, default=0, help="fewer requests than the workload names (trying it out)")
     ap.add_argument("--breakdown", action="store_true",
                     help="time by kind of kernel in an eager run with --layers layers (default 2); prints one JSON line")
