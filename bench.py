@@ -179,10 +179,10 @@ def bench_ours(args) -> dict:
                 runner.cache.allocate(i, lens[i] + 1)
                 items.append(StepItem(i, [last[i]], lens[i], [0]))
             sampling = [(0.0, n, lens[i] + 1) for n, i in enumerate(ids)]
-            if args.sync or not runner.can_launch(items):
+            if args.sync or args.eager:
                 chosen = runner.run(items, sampling)
             else:
-                handle = runner.launch(items, sampling, feed_from=flight[0])
+                handle = runner.launch(items, sampling, feed_from=flight[0], feed=list(range(len(ids))))
                 chosen = flight[0].read() if flight[0] is not None else [last[i] for i in ids]
                 flight[0] = handle
             for i, t in zip(ids, chosen):

@@ -33,6 +33,7 @@ def _add_engine_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--decode-weight-copy", dest="decode_weight_copy", action="store_true", default=None,
                     help="keep a second copy of the matrices a decode step streams, laid out per SM (default: when it fits)")
     ap.add_argument("--no-decode-weight-copy", dest="decode_weight_copy", action="store_false")
+    ap.add_argument("--profile-ranges", action="store_true", help="NVTX ranges around the step and every layer run")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--random-weights", action="store_true",
                     help="ignore the folder's safetensors and make weights on the device from --seed")
@@ -50,7 +51,7 @@ def cmd_generate(args) -> int:
               gpu_memory_utilization=args.gpu_memory_utilization, kvcache_block_size=args.kvcache_block_size,
               num_kvcache_blocks=args.num_kvcache_blocks, scheduler_policy=args.scheduler_policy,
               enforce_eager=args.enforce_eager, seed=args.seed, enable_prefix_cache=args.enable_prefix_cache,
-              decode_weight_copy=args.decode_weight_copy,
+              decode_weight_copy=args.decode_weight_copy, profile_ranges=args.profile_ranges,
               random_weights_seed=args.seed if args.random_weights else None)
     sp = SamplingParams(temperature=args.temperature, max_tokens=args.max_tokens, ignore_eos=args.ignore_eos,
                         seed=args.sampling_seed)

@@ -5,7 +5,7 @@ point fills from keyword arguments (nanovllm/engine/llm_engine.py:179-181).  The
 options that belong to its hybrid (GDN, vision, joint prefix cache) path are absent.
 Options that the reference does not have: ``dtype`` (run the checkpoint in another
 precision; ``"float32"`` is the true 32-bit path), ``seed``, ``decode_weight_copy``,
-``async_decode`` and ``poison_cache``.
+``async_decode``, ``profile_ranges`` and ``poison_cache``.
 """
 from __future__ import annotations
 
@@ -39,6 +39,8 @@ class Config:
     async_decode: bool = True                # launch a decode step before the host has read the tokens of the one before
                                              # (they are passed on on the device); an end-of-sequence token is then seen
                                              # one step late and the extra token dropped.  Needs the CUDA graphs.
+    profile_ranges: bool = False             # NVTX ranges around the step, every layer run, the final norm and the head,
+                                             # for profilers that filter or group by range
     poison_cache: bool = False               # fill the cache pools with NaN at start: a read of a slot that no step
                                              # wrote shows in the logits (tests, replay)
     dtype: str | torch.dtype | None = None   # None: the checkpoint's own

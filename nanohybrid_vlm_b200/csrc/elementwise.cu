@@ -51,6 +51,31 @@ NHV_API int nhv_embed(int dtype, void* out, const void* table, const int* ids, i
   return 0;
 }
 
+// ---------------------------------------------------------------- tokens handed from one step to the next
+// token_ids[t] = chosen[feed_src[t]] where feed_src[t] >= 0: a step that was launched before the host read the tokens
+// of the step before it takes them from that step's sampler output on the device.  Entries with feed_src[t] < 0 keep
+// the value that the host wrote.  A source row beyond the step before, or a token outside the vocabulary (which no
+// sampler writes), becomes token 0 rather than an index out of the embedding table.
+__global__ void feed_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ feed_src,
+                                   const int* __restrict__ chosen, int n_tokens, int n_chosen, int vocab) {
+  pdl_prologue();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tokens) return;
+  const int src = feed_src[t];
+  if (src < 0) return;
+  const int tok = src < n_chosen ? chosen[src] : 0;
+  token_ids[t] = tok >= 0 && tok < vocab ? tok : 0;
+}
+
+NHV_API int nhv_feed_tokens(int* token_ids, const int* feed_src, const int* chosen, int n_tokens, int n_chosen, int vocab,
+                            cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  NHV_REQUIRE(n_tokens > 0 && n_chosen > 0 && vocab > 0 && token_ids && feed_src && chosen, "feed_tokens: bad arguments");
+  nhv_launch(feed_tokens_kernel, (n_tokens + 127) / 128, 128, 0, stream, token_ids, feed_src, chosen, n_tokens, n_chosen, vocab);
+  NHV_CHECK_LAUNCH("feed_tokens");
+  return 0;
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // One block per output row.  Row r reads source row rows[r] (or r when rows is null).
 // residual != null: s = x + residual in fp32; if write_residual the rounded s replaces residual.

@@ -97,7 +97,7 @@ class BatchBuilder:
         off, sections = 0, {}
         for name, n in (("seeds", 2 * R), ("temperatures", R), ("sample_positions", R), ("token_ids", T),
                         ("positions", self.n_axes * T), ("cu_q", S + 1), ("kv_len", S), ("q_start", S),
-                        ("state_slots", S), ("logit_rows", R)):
+                        ("state_slots", S), ("logit_rows", R), ("feed_src", T)):
             sections[name] = (off, n)
             off += _align(n)
         for g in range(self.n_groups):
@@ -108,15 +108,11 @@ class BatchBuilder:
         self._layouts[key] = (sections, off)
         return sections, off
 
-    def token_ids_on_device(self, bucket: int, table_width: int) -> torch.Tensor:
-        """Where a padded step of ``bucket`` single tokens keeps its token ids on the device."""
-        sec, _ = self._layout(bucket, bucket, bucket, table_width)
-        o, n = sec["token_ids"]
-        return self._dev[o:o + n]
-
     def build(self, items: list[StepItem], table_width: int | None = None, sampling=None,
-              pad_to: int | None = None, views: bool = True) -> StepBatch | None:
+              pad_to: int | None = None, views: bool = True, feed: list[int] | None = None) -> StepBatch | None:
         """``sampling``: one (temperature, seed, position of the token being chosen) per wanted row.
+        ``feed``: per item, the row of the step before whose chosen token is this item's (single) token, or -1; the
+        arrays ``last_token_ids`` / ``last_feed_src`` then say on the device which tokens to take from there.
         ``pad_to``: for a batch of single tokens, fill up to this many requests with idle entries (one
         token that is stored nowhere and reads no page), so that the batch has a fixed shape.
         ``views`` False: only fill and copy the arrays (for the replay of a captured step) and return None."""
@@ -267,10 +263,22 @@ class BatchBuilder:
             r += 1
         if tok[:T].min() < 0 or tok[:T].max() >= self.vocab:
             raise ValueError(f"token ids must lie in [0, {self.vocab})")
+        fs = view("feed_src")
+        fs[:T] = -1
+        if feed is not None:
+            if len(feed) != n_real:
+                raise ValueError("one source row (or -1) per item is needed")
+            for s, (it, src) in enumerate(zip(items, feed)):
+                if src >= 0:
+                    if len(it.tokens) != 1:
+                        raise ValueError("only a single token can be taken from the step before")
+                    fs[cu[s]] = src
         self._dev[:total].copy_(self._host[:total], non_blocking=True)
         if self._copied is not None:
             self._copied.record()
         self.bytes_last_copy = total * 4
+        o_tok, o_feed = sec["token_ids"][0], sec["feed_src"][0]
+        self.last_token_ids, self.last_feed_src = self._dev[o_tok:o_tok + T], self._dev[o_feed:o_feed + T]
         self._table_rows = (layout_key, new_rows) if decode_only else None
         if not views:           # a replayed graph reads the arrays where they lie; nobody needs the views
             return None

@@ -141,9 +141,10 @@ class LLMEngine:
     def step(self):
         """Schedule, run one mixed batch, sample, book.  Returns (finished [(seq_id, token_ids)], StepStats).
 
-        A step of decoded tokens only is launched without waiting for it (``async_decode``): the call returns what
-        the step BEFORE it finished, and the tokens pass from one step to the next on the device.  Any other step
-        (prompt portions, a change in the set of decoding requests) first waits for the step in flight."""
+        With ``async_decode`` a step is launched without waiting for it: the call returns what the step BEFORE it
+        finished, and the tokens that the step in flight has chosen pass to this one on the device.  Only a plan that
+        needs an unread token anywhere else than as a request's single next token (a preempted request that is
+        recomputed) first waits for the step in flight."""
         t0 = perf_counter()
         outputs = []
         if self.scheduler.is_finished():
@@ -164,33 +165,61 @@ class LLMEngine:
                 return outputs, StepStats(0, 0, perf_counter() - t0)
             plan = self.scheduler.schedule()
         runner = self.model_runner
-        pure_decode = all(s.num_scheduled_tokens == 1 and s.num_cached_tokens + 1 == len(s) for s in plan.seqs)
-        items = None
-        if self.async_decode and pure_decode:
-            fed = self._inflight is not None and [s.seq_id for s in self._inflight[0]] == [s.seq_id for s in plan.seqs]
-            if self._inflight is not None and not fed:
-                outputs += self._drain()                     # other requests than the step in flight: read it first
+        if self.async_decode:
+            # Which tokens of this plan has the host not read yet, and can the step in flight hand them over?  It can
+            # if each is the single next token of a request that the step in flight chose a token for.
+            flight = self._inflight
+            source = {}
+            if flight is not None:
+                row = 0
+                for s, place in zip(flight[0], flight[1]):
+                    if place >= 0:
+                        source[s.seq_id] = (place, row)
+                        row += 1
+            feed, ok = [], True
+            for s in plan.seqs:
+                start, n = s.num_cached_tokens, s.num_scheduled_tokens
+                pending = [i for i in range(start, start + n) if s.token_ids[i] == PENDING]
+                if not pending:
+                    feed.append(-1)
+                elif n == 1 and s.seq_id in source and source[s.seq_id][0] == start:
+                    feed.append(source[s.seq_id][1])
+                else:
+                    ok = False                                # e.g. a preempted request recomputed from its first token
+                    break
+            if not ok:
+                outputs += self._drain()
+                flight, feed = None, None
             seqs = [s for s in plan.seqs if not s.is_finished]
+            if len(seqs) != len(plan.seqs):
+                feed = None if feed is None else [f for s, f in zip(plan.seqs, feed) if not s.is_finished]
             if seqs:
-                items = [StepItem(s.seq_id, [0 if s.token_ids[-1] == PENDING else s.token_ids[-1]], s.num_cached_tokens, [0])
-                         for s in seqs]
-                if not runner.can_launch(items):
-                    items = None
-            if items is not None:
+                items, sampled = [], []
                 for s in seqs:
+                    start, n = s.num_cached_tokens, s.num_scheduled_tokens
+                    last = start + n == len(s)
+                    toks = [0 if t == PENDING else t for t in s.token_ids[start:start + n]]
+                    items.append(StepItem(s.seq_id, toks, start, [n - 1] if last else []))
+                    if last:
+                        sampled.append(s)
                     m = self.request_metrics[s.seq_id]
                     if m.first_scheduled_time is None:
                         m.first_scheduled_time = t0
-                self.last_sampled_ids = [s.seq_id for s in seqs]
-                handle = runner.launch(items, [(s.temperature, s.seed, len(s)) for s in seqs],
-                                       feed_from=self._inflight[2] if fed and len(seqs) == len(plan.seqs) else None)
+                self.last_sampled_ids = [s.seq_id for s in sampled]
+                if flight is None or feed is None or all(f < 0 for f in feed):
+                    feed = None
+                handle = runner.launch(items, [(s.temperature, s.seed, len(s)) for s in sampled],
+                                       feed_from=flight[2] if feed is not None else None, feed=feed)
                 self.h2d_bytes += runner.builder.bytes_last_copy
-                self.d2h_bytes += 4 * (len(seqs) + 1)
+                self.d2h_bytes += 4 * (len(sampled) + 1)
+                n_decode = sum(1 for it in items if len(it.tokens) == 1 and it.want)
+                n_prefill = sum(len(it.tokens) for it in items) - n_decode
                 places = self.scheduler.advance(seqs)
-                previous, self._inflight = self._inflight if fed else None, (seqs, places, handle)
+                previous, self._inflight = self._inflight, (seqs, places, handle)
                 if previous is not None:
                     outputs += self._resolve(previous)
-                return outputs, StepStats(len(seqs), 0, perf_counter() - t0)
+                return outputs, StepStats(n_decode, n_prefill, perf_counter() - t0)
+            return outputs, StepStats(0, 0, perf_counter() - t0)
         # ---- the step is run and read at once
         outputs += self._drain()
         seqs = [s for s in plan.seqs if not s.is_finished]    # the step just read may have ended some of them
@@ -237,7 +266,7 @@ class LLMEngine:
         """Read the tokens of a launched step and book them."""
         seqs, places, handle = flight
         self.scheduler.resolve(seqs, places, handle.read())
-        return self._book(seqs, perf_counter())
+        return self._book([s for s, place in zip(seqs, places) if place >= 0], perf_counter())
 
     def abort_all(self) -> None:
         """Drop every request (waiting, running or in flight) and give back what they hold."""

@@ -117,8 +117,12 @@ class CausalLM:
         return needs
 
     # ------------------------------------------------------------------ one step
+    profile_ranges = False      # set by the runner from the engine option of that name
+
     def forward(self, batch, storage) -> torch.Tensor:
         """Run the batch's tokens through every layer run; returns fp32 logits [wanted rows, vocab]."""
+        if self.profile_ranges:
+            return self._forward_with_ranges(batch, storage)
         h = self.embedding.forward(batch.token_ids, batch)
         for pos in self.positions:
             h = pos.add_to_embeddings(h, batch)
@@ -130,3 +134,30 @@ class CausalLM:
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=self.device)
         x = self.final_norm.forward_add_rows(h, residual, batch.logit_rows)
         return self.head.forward(x)
+
+    def _forward_with_ranges(self, batch, storage) -> torch.Tensor:
+        """``forward`` with an NVTX range around the step ("step T=<tokens> S=<requests>"), the embedding, every
+        layer run ("run <i> layer <j>"), and the final norm with the head."""
+        nvtx = torch.cuda.nvtx
+        nvtx.range_push(f"step T={batch.n_tokens} S={batch.n_seqs}")
+        try:
+            nvtx.range_push("embedding")
+            h = self.embedding.forward(batch.token_ids, batch)
+            for pos in self.positions:
+                h = pos.add_to_embeddings(h, batch)
+            nvtx.range_pop()
+            residual = None
+            for i, run in enumerate(self.spec.order):
+                nvtx.range_push(f"run {i} layer {run.layer}")
+                view = storage.view(i, run.cache_from, batch)
+                h, residual = self.blocks[run.layer].forward(h, residual, batch, view)
+                nvtx.range_pop()
+            if batch.n_logit_rows == 0:
+                return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=self.device)
+            nvtx.range_push("final norm and head")
+            x = self.final_norm.forward_add_rows(h, residual, batch.logit_rows)
+            logits = self.head.forward(x)
+            nvtx.range_pop()
+            return logits
+        finally:
+            nvtx.range_pop()

@@ -19,17 +19,18 @@ from .model import CausalLM
 
 
 class InFlight:
-    """A launched decode step: its chosen tokens are on the device (``device_tokens``, overwritten by the next
-    replay of the same bucket) and on their way to pinned host memory."""
+    """A launched step: its chosen tokens are on the device (``device_tokens``: ``n`` tokens, then, at index
+    ``width``, the step's health word; a captured graph's buffer is overwritten by the next replay of its bucket)
+    and on their way to pinned host memory."""
 
-    def __init__(self, runner, n: int, bucket: int, device_tokens: torch.Tensor, slot):
-        self.runner, self.n, self.bucket, self.device_tokens, self._slot = runner, n, bucket, device_tokens, slot
+    def __init__(self, n: int, width: int, device_tokens: torch.Tensor, slot):
+        self.n, self.width, self.device_tokens, self._slot = n, width, device_tokens, slot
 
     def read(self) -> list[int]:
         """Wait for the step and return its tokens (raises ``KernelError`` if a bounded wait of a kernel ran out)."""
         buf, event = self._slot
         event.synchronize()
-        host = buf[:self.bucket + 1].tolist()
+        host = buf[:self.width + 1].tolist()
         return ModelRunner._checked(host[:self.n] + host[-1:])
 
 
@@ -44,6 +45,7 @@ class ModelRunner:
         self.dtype = config.dtype
         spec = config.architecture.build_spec(config.model_config)
         self.model = CausalLM(spec, self.dtype, self.device)
+        self.model.profile_ranges = bool(config.profile_ranges)
         if random_weights_seed is None:
             load_weights(self.model, config.model)
         else:
@@ -172,39 +174,48 @@ class ModelRunner:
         out since the last check.  Synchronises the device."""
         ops.raise_wait_errors()
 
-    # ------------------------------------------------------------------ a decode step whose tokens are read later
-    def can_launch(self, items: list[StepItem]) -> bool:
-        """True if ``launch`` takes these items: single tokens that all want their logits, within a graph bucket."""
-        return self._bucket(items) is not None
-
+    # ------------------------------------------------------------------ a step whose tokens are read later
     @torch.no_grad()
-    def launch(self, items: list[StepItem], sampling, feed_from: "InFlight | None" = None) -> "InFlight":
-        """Start a step of single tokens (the captured graph of its bucket) and return at once; ``InFlight.read()``
-        gives its tokens later.  ``feed_from``: the step before it, still in flight, over the same requests in the
-        same order: every item's token is then taken on the device from that step's chosen tokens (the items' own
-        token values are place-holders), so the host need not have read them."""
+    def launch(self, items: list[StepItem], sampling, feed_from: "InFlight | None" = None,
+               feed: list[int] | None = None) -> "InFlight":
+        """Start a step and return at once; ``InFlight.read()`` gives the tokens it chose, one per wanted row, later.
+        ``feed_from`` / ``feed``: the step before it, still in flight, and per item the row of that step whose
+        chosen token is the item's single token (-1: the item brings its own): such tokens are taken on the device
+        (the values in the items are place-holders), so the host need not have read them.  A batch of single
+        tokens replays the captured graph of its size bucket; anything else runs eagerly."""
+        if feed_from is None:
+            feed = None
         bucket = self._bucket(items)
+        slot = self._host_tokens[self._host_turn]
+        self._host_turn ^= 1
         if bucket is None:
-            raise ValueError("launch takes single tokens that all want their logits, within a graph bucket")
+            batch = self.builder.build(items, sampling=sampling, feed=feed)
+            if feed is not None:
+                ops.feed_tokens(batch.token_ids, self.builder.last_feed_src, feed_from.device_tokens, self.vocab_size)
+            logits = self.model.forward(batch, self.storage)
+            n = batch.n_logit_rows
+            tokens = torch.empty(n + 1, dtype=torch.int32, device=self.device)      # tokens, health word
+            ops.sample(tokens, logits, batch.temperatures, batch.seeds, batch.sample_positions)
+            self.last_logits = logits
+            if n + 1 > slot[0].numel():
+                slot = (torch.empty(n + 1, dtype=torch.int32, pin_memory=True), slot[1])
+            slot[0][:n + 1].copy_(tokens, non_blocking=True)
+            slot[1].record()
+            return InFlight(n, n, tokens, slot)
         if bucket not in self._graphs:
             self._capture(bucket)
         graph, tokens, launches, logits = self._graphs[bucket]
         n = len(items)
-        self.builder.build(items, table_width=self.max_pages_per_seq, sampling=sampling, pad_to=bucket, views=False)
-        if feed_from is not None:
-            if feed_from.n != n or feed_from.bucket != bucket:
-                raise ValueError("a step can only be fed by a step over the same requests")
-            # the tokens that the step before chose, straight into this step's token ids (after the host's copy of
-            # the batch arrays, before the graph that reads them)
-            self.builder.token_ids_on_device(bucket, self.max_pages_per_seq)[:n].copy_(feed_from.device_tokens[:n])
+        self.builder.build(items, table_width=self.max_pages_per_seq, sampling=sampling, pad_to=bucket, views=False, feed=feed)
+        if feed is not None:
+            # between the host's copy of the batch arrays and the graph that reads them
+            ops.feed_tokens(self.builder.last_token_ids, self.builder.last_feed_src, feed_from.device_tokens, self.vocab_size)
         graph.replay()
         library.LAUNCHES += launches
         self.last_logits = logits[:n]
-        slot = self._host_tokens[self._host_turn]
-        self._host_turn ^= 1
         slot[0][:bucket + 1].copy_(tokens, non_blocking=True)     # tokens and health word, before the next replay overwrites them
         slot[1].record()
-        return InFlight(self, n, bucket, tokens, slot)
+        return InFlight(n, bucket, tokens, slot)
 
     def _bucket(self, items) -> int | None:
         if not self.graph_buckets or len(items) > self.graph_buckets[-1]:

@@ -156,14 +156,21 @@ class Scheduler:
 
     # ------------------------------------------------------------------ a step whose tokens are read later
     def advance(self, seqs: list[Sequence]) -> list[int]:
-        """Book a launched step of single tokens whose chosen tokens are still on the device: every request gets a
-        place for its token (``PENDING``) so that the next step can be planned, and a request that has reached its
-        length leaves ``running`` (its cache is kept until ``resolve`` sees its last token).  Returns, per request,
-        the index of the place in its token list."""
+        """Book a launched step whose chosen tokens are still on the device.  A request whose portion did not reach
+        its end just moves on.  One that did gets a place for its token (``PENDING``) so that the next step can
+        be planned; if it has reached its length it leaves ``running`` (its cache is kept until ``resolve`` sees its
+        last token).  Returns, per request, the index of the place in its token list (-1: no token was chosen)."""
         places = []
         for seq in seqs:
             seq.num_cached_tokens += seq.num_scheduled_tokens
             seq.num_scheduled_tokens = 0
+            if seq.num_cached_tokens < len(seq):
+                places.append(-1)
+                if self.cache.prefix_cache:
+                    self.cache.commit(seq.seq_id, seq.token_ids, seq.num_cached_tokens)
+                if self.cache.has_windows:
+                    self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
+                continue
             places.append(len(seq))
             seq.append_token(PENDING)
             if seq.num_completion_tokens >= seq.max_tokens or len(seq) >= self.max_model_len:
@@ -174,10 +181,15 @@ class Scheduler:
         return places
 
     def resolve(self, seqs: list[Sequence], places: list[int], token_ids: list[int]) -> None:
-        """The tokens of a step booked with ``advance`` have arrived: they take their places; a request stops at
+        """The tokens of a step booked with ``advance`` have arrived (one per request that has a place, in the order
+        of the requests): they take their places; a request stops at
         the end-of-sequence token (whatever a later step, launched meanwhile, computed for it is dropped) or at
         its length."""
-        for seq, place, token in zip(seqs, places, token_ids):
+        tokens = iter(token_ids)
+        for seq, place in zip(seqs, places):
+            if place < 0:
+                continue                                      # a portion that did not reach its request's end
+            token = next(tokens)
             if seq.is_finished or place >= len(seq):
                 continue                                      # it ended at an earlier token while this step ran
             seq.token_ids[place] = token

@@ -19,6 +19,7 @@ P, I, F = c_void_p, c_int, c_float
 _SIGNATURES = {
     # name: argtypes (all return int)
     "nhv_embed": [I, P, P, P, I, I, I, P],
+    "nhv_feed_tokens": [P, P, P, I, I, I, P],
     "nhv_rmsnorm": [I, P, P, P, P, P, I, I, F, I, F, P],
     "nhv_silu_mul": [I, P, P, I, I, P],
     "nhv_to_f32": [I, P, P, c_size_t, P],

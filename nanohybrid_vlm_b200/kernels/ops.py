@@ -54,6 +54,15 @@ def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
          table.shape[1], table.shape[0], stream_ptr())
 
 
+def feed_tokens(token_ids, feed_src, chosen, vocab: int) -> None:
+    """token_ids[t] = chosen[feed_src[t]] where feed_src[t] >= 0 (tokens that the step before chose, taken on the
+    device); the other entries keep what the host wrote."""
+    _need_cuda(token_ids, feed_src, chosen)
+    assert token_ids.dtype == feed_src.dtype == chosen.dtype == torch.int32 and feed_src.numel() >= token_ids.numel()
+    call("nhv_feed_tokens", token_ids.data_ptr(), feed_src.data_ptr(), chosen.data_ptr(), token_ids.numel(), chosen.numel(),
+         int(vocab), stream_ptr())
+
+
 def rmsnorm(out, x, weight, eps: float, residual=None, rows=None, write_residual: bool = True,
             weight_offset: float = 0.0) -> None:
     """out[r] = norm(x[src] (+ residual[src])) * (weight + weight_offset), src = rows[r] or r.

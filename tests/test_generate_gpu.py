@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 def make_llm(model_dir, name, dtype="float32", **kw):
     from nanohybrid_vlm_b200 import LLM
     opts = dict(dtype=dtype, kvcache_block_size=16 if name == "A" else 8, num_kvcache_blocks=128, max_num_seqs=8,
-                max_num_batched_tokens=64, max_model_len=TINY[name][0]["max_position_embeddings"])
+                max_num_batched_tokens=64, max_model_len=TINY[name][0]["max_position_embeddings"],
+                poison_cache=True)            # the pools start as NaN: a read of a slot that no step wrote shows
     opts.update(kw)
     return LLM(model_dir, **opts)
 
@@ -207,3 +208,12 @@ def test_decode_steps_launched_ahead_give_the_same_tokens(name, model_dirs, plai
         assert llm.scheduler.num_preemptions > 0
         del llm
     assert outs[0] == outs[1]
+
+
+def test_profile_ranges_leave_tokens_unchanged(model_dirs, plain_models):
+    """``profile_ranges``: the step, the layer runs and the head stand in NVTX ranges; the numbers are the same."""
+    from nanohybrid_vlm_b200 import SamplingParams
+    prompts = prompts_for("B", (9, 21), seed=31)
+    llm = make_llm(model_dirs["B"], "B", profile_ranges=True)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True), use_tqdm=False)
+    assert [o["token_ids"] for o in out] == [plain_models["B"].greedy(p, 5) for p in prompts]
