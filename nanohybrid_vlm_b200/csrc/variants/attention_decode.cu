@@ -12,7 +12,8 @@
 //    from the paged pool (the pool seen as one matrix [pages * 2 * kv_heads * page_size, D]; boxes of 64 columns x
 //    32 keys in the 128-byte swizzle; plain per-block copies, no multicast; completion counted in bytes on an
 //    mbarrier).  It looks the pages of 32 tiles up at a time and runs ahead of the consumers across the borders of
-//    requests, so the ring never drains: up to STAGES * 2 * 32 * D * 2 bytes are in flight per SM.
+//    requests, so the ring never drains: up to 12 stages of 2 * 32 * D * 2 bytes
+//    (192 KB at head size 128) are in flight per SM.
 //  * The consumer warps (four for head sizes up to 128) take whole tiles in turn (tile t of the block goes to warp
 //    t % NCW): no warp waits for another while a piece lasts.  mma.sync.m16n8k16 bf16 with fp32 accumulation, online softmax in fp32 on base-2
 //    exponents, the rows being the query heads of the group (padded to 16).  At the end of a piece (a block's tiles
@@ -61,14 +62,16 @@ constexpr int STAGE_BYTES = 2 * TILE_BYTES;
 // one another, so it can never ask for a phase while the one before it is still filling (a wait by parity cannot
 // tell those two apart).  Every warp has two stages, so its next tile is on its way while it works on one.
 constexpr int NCW = D <= 128 ? 4 : (D == 192 ? 3 : 2);
-constexpr int STAGES = 2 * NCW;
-static_assert(STAGES % NCW == 0, "every stage must belong to one consumer warp");
+constexpr int STAGES_MIN = 2 * NCW;
+// Groups of up to 8 query heads need only 8 rows of the merge buffer: the room goes to the ring (three stages a warp).
+constexpr int STAGES_DEEP = D <= 128 ? 3 * NCW : STAGES_MIN;
 constexpr int THREADS = (NCW + 1) * 32;
 constexpr int Q_BYTES = 16 * D * 2;
-constexpr int MERGE_BYTES = NCW * 16 * D * 4 + NCW * 16 * 2 * 4;
+constexpr int merge_bytes(int mrows) { return NCW * mrows * D * 4 + NCW * mrows * 2 * 4; }
 constexpr int MAX_SEQS = 512;
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + MERGE_BYTES + Q_BYTES;
-static_assert(SMEM_BYTES + 8 * 1024 <= 227 * 1024, "ring, merge buffer and queries must fit one block's shared memory");
+constexpr size_t smem_bytes(int stages, int mrows) { return 1024 + (size_t)stages * STAGE_BYTES + merge_bytes(mrows) + Q_BYTES; }
+static_assert(smem_bytes(STAGES_MIN, 16) + 8 * 1024 <= 227 * 1024 && smem_bytes(STAGES_DEEP, 8) + 8 * 1024 <= 227 * 1024,
+              "ring, merge buffer and queries must fit one block's shared memory");
 constexpr int MIN_TILES = 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -253,13 +256,16 @@ struct Piece {
   long long first;          // first tile (in the flat list) of this piece's (request, head block)
 };
 
+// STAGES: ring stages (a multiple of NCW); MROWS: rows of the merge buffer (16, or 8 for groups of up to 8 heads).
+template <int STAGES, int MROWS>
 __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_constant__ Params p) {
+  static_assert(STAGES % NCW == 0, "every stage must belong to one consumer warp");
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = smem_unaligned + ((1024 - (smem_u32(smem_unaligned) & 1023)) & 1023);
   unsigned char* ring = smem;                                                   // [STAGES][K tile | V tile]
-  float* mo = reinterpret_cast<float*>(smem + (size_t)STAGES * STAGE_BYTES);    // [NCW][16][D]
-  float* mml = mo + NCW * 16 * D;                                               // [NCW][16][2]
-  bf16* qbuf = reinterpret_cast<bf16*>(mml + NCW * 16 * 2);                     // [16][D], chunks exchanged as in a tile
+  float* mo = reinterpret_cast<float*>(smem + (size_t)STAGES * STAGE_BYTES);    // [NCW][MROWS][D]
+  float* mml = mo + NCW * MROWS * D;                                            // [NCW][MROWS][2]
+  bf16* qbuf = reinterpret_cast<bf16*>(mml + NCW * MROWS * 2);                  // [16][D], chunks exchanged as in a tile
   __shared__ __align__(16) bf16 s_new[2][D];                  // the new token's key and value (fused form)
   __shared__ unsigned short s_cnt[MAX_SEQS];                 // tiles of each request (0: not a single-token request)
   __shared__ int s_prefix[MAX_SEQS + 1];
@@ -520,13 +526,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       l += __shfl_xor_sync(0xffffffffu, l, 2);
       const int R = (lane >> 2) + 8 * i;
       if (R >= gn) continue;                                   // rows beyond the group hold nothing
-      float* dst = mo + ((size_t)warp * 16 + R) * D + ((lane & 3) << 1);
+      float* dst = mo + ((size_t)warp * MROWS + R) * D + ((lane & 3) << 1);
 #pragma unroll
       for (int n = 0; n < DN; ++n)
         *reinterpret_cast<float2*>(dst + n * 8) = make_float2(st.o[n][2 * i], st.o[n][2 * i + 1]);
       if ((lane & 3) == 0) {
-        mml[(warp * 16 + R) * 2] = st.m[i];
-        mml[(warp * 16 + R) * 2 + 1] = l;
+        mml[(warp * MROWS + R) * 2] = st.m[i];
+        mml[(warp * MROWS + R) * 2 + 1] = l;
       }
     }
     consumer_sync();
@@ -539,16 +545,16 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       const int R = id / (D / 4), c4 = id - R * (D / 4);
       float M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < NCW; ++w) M = fmaxf(M, mml[(w * 16 + R) * 2]);
+      for (int w = 0; w < NCW; ++w) M = fmaxf(M, mml[(w * MROWS + R) * 2]);
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       float L = 0.f;
 #pragma unroll
       for (int w = 0; w < NCW; ++w) {
-        const float mw = mml[(w * 16 + R) * 2];
+        const float mw = mml[(w * MROWS + R) * 2];
         const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-        const float4 t = *reinterpret_cast<const float4*>(mo + ((size_t)w * 16 + R) * D + c4 * 4);
+        const float4 t = *reinterpret_cast<const float4*>(mo + ((size_t)w * MROWS + R) * D + c4 * 4);
         acc.x += t.x * f; acc.y += t.y * f; acc.z += t.z * f; acc.w += t.w * f;
-        L += mml[(w * 16 + R) * 2 + 1] * f;
+        L += mml[(w * MROWS + R) * 2 + 1] * f;
       }
       if (whole) {
         const float inv = L > 0.f ? 1.0f / L : 0.f;
@@ -707,10 +713,15 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
     }
     p.pool_map = it->second.second;
   }
+  const bool deep = nq / nkv <= 8;                           // groups of up to 8 heads: the smaller merge buffer, the deeper ring
+  const size_t smem = deep ? smem_bytes(STAGES_DEEP, 8) : smem_bytes(STAGES_MIN, 16);
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess) {
-      snprintf(g_err, sizeof(g_err), "attention (decode, TMA): cannot reserve %zu bytes of shared memory", SMEM_BYTES);
+    if (cudaFuncSetAttribute(attn_decode_kernel<STAGES_DEEP, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem_bytes(STAGES_DEEP, 8)) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_decode_kernel<STAGES_MIN, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem_bytes(STAGES_MIN, 16)) != cudaSuccess) {
+      snprintf(g_err, sizeof(g_err), "attention (decode, TMA): cannot reserve %zu bytes of shared memory", smem);
       return 2;
     }
     attr_set = true;
@@ -729,8 +740,9 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nq = nq; p.nkv = nkv;
   p.page_size = page_size; p.n_pages = n_pages; p.window = window;
   p.scale_log2 = scale * LOG2E;
-  if (nhv_launch(attn_decode_kernel, dim3(blocks), dim3(THREADS), SMEM_BYTES, stream, p) != cudaSuccess ||
-      cudaPeekAtLastError() != cudaSuccess) {
+  const cudaError_t launched = deep ? nhv_launch(attn_decode_kernel<STAGES_DEEP, 8>, dim3(blocks), dim3(THREADS), smem, stream, p)
+                                    : nhv_launch(attn_decode_kernel<STAGES_MIN, 16>, dim3(blocks), dim3(THREADS), smem, stream, p);
+  if (launched != cudaSuccess || cudaPeekAtLastError() != cudaSuccess) {
     snprintf(g_err, sizeof(g_err), "attention (decode, TMA): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return 2;
   }
