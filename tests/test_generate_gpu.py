@@ -217,3 +217,57 @@ def test_profile_ranges_leave_tokens_unchanged(model_dirs, plain_models):
     llm = make_llm(model_dirs["B"], "B", profile_ranges=True)
     out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True), use_tqdm=False)
     assert [o["token_ids"] for o in out] == [plain_models["B"].greedy(p, 5) for p in prompts]
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_requests_arriving_while_others_run_give_the_same_tokens_launched_ahead_or_not(seed, model_dirs, plain_models):
+    """Random lives: requests of random lengths arrive between steps, with random limits, some stopping at an
+    end-of-sequence token, some sampled with a temperature, prompts that share leading pages, in a pool so small
+    that requests wait and are preempted.  With decode steps launched ahead of the read and with every step read at
+    once the same tokens come out, and the greedy ones are the plain model's."""
+    import random
+    from nanohybrid_vlm_b200 import SamplingParams
+    name = "B"
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(seed)
+    stem = [rng.randrange(vocab) for _ in range(40)]
+    jobs = []
+    for i in range(14):
+        n = rng.choice((1, 2, 7, 8, 9, 23, 40, 57))
+        prompt = (stem[:n] if rng.random() < 0.4 else [rng.randrange(vocab) for _ in range(n)])
+        greedy = rng.random() < 0.6
+        sp = SamplingParams(temperature=0.0 if greedy else 0.9, max_tokens=rng.choice((1, 2, 5, 11, 16)),
+                            ignore_eos=rng.random() < 0.5, seed=1000 + i)
+        jobs.append((rng.randrange(0, 30), prompt, sp))            # (the step before which it arrives, prompt, params)
+    ref0 = plain_models[name].greedy(jobs[0][1], 4)
+    eos = ref0[-1]
+    results = []
+    for async_decode in (True, False):
+        llm = make_llm(model_dirs[name], name, eos=eos, async_decode=async_decode, num_kvcache_blocks=22, max_num_seqs=5,
+                       max_portion=13, max_num_batched_tokens=48)
+        ids, done, step = {}, {}, 0
+        todo = sorted(range(len(jobs)), key=lambda j: jobs[j][0])
+        while todo or not llm.is_finished():
+            while todo and (jobs[todo[0]][0] <= step or llm.is_finished()):
+                j = todo.pop(0)
+                ids[llm.add_request(list(jobs[j][1]), jobs[j][2])] = j
+            finished, _ = llm.step()
+            for seq_id, tokens in finished:
+                assert ids[seq_id] not in done
+                done[ids[seq_id]] = tokens
+            step += 1
+            assert step < 2000
+        assert len(done) == len(jobs)
+        llm.model_runner.cache.check()
+        assert all(p.num_free == p.num_pages for p in llm.model_runner.cache.pools)
+        results.append(done)
+        del llm
+    assert results[0] == results[1]
+    for j, (_, prompt, sp) in enumerate(jobs):
+        got = results[0][j]
+        assert 1 <= len(got) <= sp.max_tokens
+        if sp.temperature == 0.0:
+            want = plain_models[name].greedy(prompt, sp.max_tokens)
+            if not sp.ignore_eos and eos in want:
+                want = want[:want.index(eos) + 1]
+            assert got == want, f"job {j}"
