@@ -144,7 +144,8 @@ class LLMEngine:
         With ``async_decode`` a step is launched without waiting for it: the call returns what the step BEFORE it
         finished, and the tokens that the step in flight has chosen pass to this one on the device.  Only a plan that
         needs an unread token anywhere else than as a request's single next token (a preempted request that is
-        recomputed) first waits for the step in flight."""
+        recomputed) first waits for the step in flight.  Without it the step is read before the call returns.
+        After a ``KernelError`` the requests of the failed step hold no valid tokens: ``abort_all()`` drops them."""
         t0 = perf_counter()
         outputs = []
         if self.scheduler.is_finished():
@@ -165,90 +166,61 @@ class LLMEngine:
                 return outputs, StepStats(0, 0, perf_counter() - t0)
             plan = self.scheduler.schedule()
         runner = self.model_runner
-        if self.async_decode:
-            # Which tokens of this plan has the host not read yet, and can the step in flight hand them over?  It can
-            # if each is the single next token of a request that the step in flight chose a token for.
-            flight = self._inflight
-            source = {}
-            if flight is not None:
-                row = 0
-                for s, place in zip(flight[0], flight[1]):
-                    if place >= 0:
-                        source[s.seq_id] = (place, row)
-                        row += 1
-            feed, ok = [], True
-            for s in plan.seqs:
-                start, n = s.num_cached_tokens, s.num_scheduled_tokens
-                pending = [i for i in range(start, start + n) if s.token_ids[i] == PENDING]
-                if not pending:
-                    feed.append(-1)
-                elif n == 1 and s.seq_id in source and source[s.seq_id][0] == start:
-                    feed.append(source[s.seq_id][1])
-                else:
-                    ok = False                                # e.g. a preempted request recomputed from its first token
-                    break
-            if not ok:
-                outputs += self._drain()
-                flight, feed = None, None
-            seqs = [s for s in plan.seqs if not s.is_finished]
-            if len(seqs) != len(plan.seqs):
-                feed = None if feed is None else [f for s, f in zip(plan.seqs, feed) if not s.is_finished]
-            if seqs:
-                items, sampled = [], []
-                for s in seqs:
-                    start, n = s.num_cached_tokens, s.num_scheduled_tokens
-                    last = start + n == len(s)
-                    toks = [0 if t == PENDING else t for t in s.token_ids[start:start + n]]
-                    items.append(StepItem(s.seq_id, toks, start, [n - 1] if last else []))
-                    if last:
-                        sampled.append(s)
-                    m = self.request_metrics[s.seq_id]
-                    if m.first_scheduled_time is None:
-                        m.first_scheduled_time = t0
-                self.last_sampled_ids = [s.seq_id for s in sampled]
-                if flight is None or feed is None or all(f < 0 for f in feed):
-                    feed = None
-                handle = runner.launch(items, [(s.temperature, s.seed, len(s)) for s in sampled],
-                                       feed_from=flight[2] if feed is not None else None, feed=feed)
-                self.h2d_bytes += runner.builder.bytes_last_copy
-                self.d2h_bytes += 4 * (len(sampled) + 1)
-                n_decode = sum(1 for it in items if len(it.tokens) == 1 and it.want)
-                n_prefill = sum(len(it.tokens) for it in items) - n_decode
-                places = self.scheduler.advance(seqs)
-                previous, self._inflight = self._inflight, (seqs, places, handle)
-                if previous is not None:
-                    outputs += self._resolve(previous)
-                return outputs, StepStats(n_decode, n_prefill, perf_counter() - t0)
+        # Which tokens of this plan has the host not read yet, and can the step in flight hand them over?  It can if
+        # each is the single next token of a request that the step in flight chose a token for.
+        flight = self._inflight
+        source = {}
+        if flight is not None:
+            row = 0
+            for s, place in zip(flight[0], flight[1]):
+                if place >= 0:
+                    source[s.seq_id] = (place, row)
+                    row += 1
+        feed = []
+        for s in plan.seqs:
+            start, n = s.num_cached_tokens, s.num_scheduled_tokens
+            if PENDING not in s.token_ids[start:start + n]:
+                feed.append(-1)
+            elif n == 1 and s.seq_id in source and source[s.seq_id][0] == start:
+                feed.append(source[s.seq_id][1])
+            else:
+                feed = None                                   # e.g. a preempted request recomputed from its first token
+                break
+        if feed is None:
+            outputs += self._drain()
+            flight = None
+        seqs = [s for s in plan.seqs if not s.is_finished]    # a step just read may have ended some of them
+        if len(seqs) != len(plan.seqs) or feed is None or all(f < 0 for f in feed):
+            feed = None                                       # (requests end only when a step is read, and then nothing is fed)
+        if not seqs:
+            self.last_sampled_ids = []
             return outputs, StepStats(0, 0, perf_counter() - t0)
-        # ---- the step is run and read at once
-        outputs += self._drain()
-        seqs = [s for s in plan.seqs if not s.is_finished]    # the step just read may have ended some of them
         items, sampled = [], []
-        for seq in seqs:
-            start, n = seq.num_cached_tokens, seq.num_scheduled_tokens
-            last = start + n == len(seq)
-            items.append(StepItem(seq.seq_id, seq.token_ids[start:start + n], start, [n - 1] if last else []))
+        for s in seqs:
+            start, n = s.num_cached_tokens, s.num_scheduled_tokens
+            last = start + n == len(s)
+            items.append(StepItem(s.seq_id, [0 if t == PENDING else t for t in s.token_ids[start:start + n]], start,
+                                  [n - 1] if last else []))
             if last:
-                sampled.append(seq)
-            m = self.request_metrics[seq.seq_id]
+                sampled.append(s)
+            m = self.request_metrics[s.seq_id]
             if m.first_scheduled_time is None:
                 m.first_scheduled_time = t0
-        if not items:
-            return outputs, StepStats(0, 0, perf_counter() - t0)
-        tokens = {}
         self.last_sampled_ids = [s.seq_id for s in sampled]
-        if sampled:
-            chosen = runner.run(items, [(s.temperature, s.seed, len(s)) for s in sampled])
-            self.d2h_bytes += 4 * (len(sampled) + 1)        # the tokens and the step's health word
-            tokens = {s.seq_id: t for s, t in zip(sampled, chosen)}
-        else:
-            runner.step(items)
+        handle = runner.launch(items, [(s.temperature, s.seed, len(s)) for s in sampled],
+                               feed_from=flight[2] if feed is not None else None, feed=feed)
         self.h2d_bytes += runner.builder.bytes_last_copy
-        self.scheduler.postprocess(seqs, [tokens.get(s.seq_id) for s in seqs])
-        outputs += self._book(sampled, perf_counter())
-        n_decode = sum(1 for s in seqs if s in sampled and len(items[seqs.index(s)].tokens) == 1)
-        return outputs, StepStats(plan.num_decode_tokens if len(seqs) == len(plan.seqs) else n_decode,
-                                  plan.num_prefill_tokens, perf_counter() - t0)
+        self.d2h_bytes += 4 * (len(sampled) + 1)              # the tokens and the step's health word
+        n_decode = sum(1 for it in items if len(it.tokens) == 1 and it.want)
+        stats = StepStats(n_decode, sum(len(it.tokens) for it in items) - n_decode, 0.0)
+        places = self.scheduler.advance(seqs)
+        previous, self._inflight = self._inflight, (seqs, places, handle)
+        if previous is not None:
+            outputs += self._resolve(previous)
+        if not self.async_decode:
+            outputs += self._drain()                          # every step is read before the next is planned
+        stats.elapsed = perf_counter() - t0
+        return outputs, stats
 
     def _book(self, sampled: list[Sequence], now: float) -> list:
         outputs = []

@@ -211,27 +211,12 @@ class Scheduler:
         if seq in self.waiting:
             self.waiting.remove(seq)
 
-    # ------------------------------------------------------------------ after the step
+    # ------------------------------------------------------------------ after a step that is read at once
     def postprocess(self, seqs: list[Sequence], token_ids: list[int | None]) -> None:
         """``token_ids[i]`` is the token chosen for ``seqs[i]``, or None if its portion did not reach the
-        end of the request (nothing was sampled for it)."""
+        end of the request (nothing was sampled for it): ``advance`` and ``resolve`` in one."""
         for seq, token in zip(seqs, token_ids):
-            seq.num_cached_tokens += seq.num_scheduled_tokens
-            seq.num_scheduled_tokens = 0
-            if self.cache.prefix_cache:
-                self.cache.commit(seq.seq_id, seq.token_ids, seq.num_cached_tokens)
-            if seq.num_cached_tokens < len(seq):
-                if self.cache.has_windows:
-                    self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
-                continue
-            if token is None:
+            if token is None and seq.num_cached_tokens + seq.num_scheduled_tokens == len(seq):
                 raise RuntimeError(f"request {seq.seq_id}: its last token was computed but no token was chosen")
-            seq.append_token(token)
-            done = (not seq.ignore_eos and token == self.eos) or seq.num_completion_tokens >= seq.max_tokens \
-                or len(seq) >= self.max_model_len
-            if done:
-                seq.status = SequenceStatus.FINISHED
-                self.cache.free(seq.seq_id)
-                self.running.remove(seq)
-            elif self.cache.has_windows:
-                self.cache.release_behind_window(seq.seq_id, seq.num_cached_tokens)
+        places = self.advance(seqs)
+        self.resolve(seqs, places, [t for t, place in zip(token_ids, places) if place >= 0])
