@@ -594,3 +594,49 @@ def test_attention_of_more_requests_than_the_tensor_core_kernels_plan_for(ops):
                             cu_q=dev(torch.arange(S + 1, dtype=torch.int32)), kv_len=dev(torch.tensor(lens, dtype=torch.int32)))
     ops.attention(out, dev(q_all), dev(pages), SimpleNamespace(block_tables=dev(bt)), batch, nq, nkv, d, d ** -0.5)
     torch.testing.assert_close(out.cpu().float(), torch.cat(refs).reshape(S, nq * d).float(), rtol=2e-2, atol=2e-2)
+
+
+def test_attention_decode_one_long_request_split_over_many_blocks(ops):
+    """One request of 20,000 keys beside a short one: every (request, KV head) is cut into about twenty pieces
+    that as many blocks hand to the one that arrives last; against the float64 reference."""
+    nq, nkv, d, page = 8, 2, 128, 256
+    g = torch.Generator().manual_seed(9)
+    lens = [20000, 5]
+    S = len(lens)
+    n_pages = sum(-(-L // page) for L in lens) + 1
+    pages = torch.full((n_pages, 2, nkv, page, d), float("nan")).to(torch.bfloat16)
+    rng = np.random.default_rng(9)
+    free = list(rng.permutation(n_pages))
+    tables, qs, refs = [], [], []
+    for L in lens:
+        k = torch.randn(L, nkv, d, generator=g).to(torch.bfloat16)
+        v = torch.randn(L, nkv, d, generator=g).to(torch.bfloat16)
+        q = torch.randn(1, nq, d, generator=g).to(torch.bfloat16)
+        if L > 100:
+            q[0] = 0
+            q[0, :, 3] = 6.0
+            k[7, :, 3] = 8.0                                  # a far key that stands out
+            v[7] = 3.0
+        ids = [int(free.pop()) for _ in range(-(-L // page))]
+        kp = torch.full((len(ids) * page, nkv, d), float("nan")).to(torch.bfloat16)
+        vp = kp.clone()
+        kp[:L], vp[:L] = k, v
+        pages[ids, 0] = kp.view(len(ids), page, nkv, d).transpose(1, 2)
+        pages[ids, 1] = vp.view(len(ids), page, nkv, d).transpose(1, 2)
+        tables.append(ids)
+        qs.append(q)
+        # the reference in slices of heads would be slow over 20,000 keys: one matrix product per KV head
+        G = nq // nkv
+        kk, vv = k.double(), v.double()
+        sc = torch.einsum("hd,thd->ht", q[0].double(), kk.repeat_interleave(G, 1)) * d ** -0.5
+        refs.append(torch.einsum("ht,thd->hd", torch.softmax(sc, -1), vv.repeat_interleave(G, 1)).reshape(1, nq * d))
+    width = max(len(t) for t in tables)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    q_all = torch.cat(qs).reshape(S, nq * d)
+    out = torch.full_like(q_all, float("nan"), device="cuda")
+    ops.attention_tensor_core(out, dev(q_all), dev(pages), dev(bt), dev(torch.arange(S + 1, dtype=torch.int32)),
+                              dev(torch.tensor(lens, dtype=torch.int32)), S, 0, 0, S, max(lens), nq, nkv, d, d ** -0.5, 0)
+    torch.testing.assert_close(out.cpu().float(), torch.cat(refs).float(), rtol=2e-2, atol=2e-2)
+    assert ops.take_wait_errors() == []
