@@ -6,8 +6,11 @@
 // around keeping HBM busy:
 //
 //  * Persistent, one block per SM.  The work is the flat list of 32-key tiles of every (request with one new token,
-//    block of up to 16 query heads of one KV head), request-major; block c owns the contiguous tiles
-//    [c * T / NB, (c + 1) * T / NB), so every SM reads the same number of bytes whatever the batch looks like.
+//    block of up to 16 query heads of one KV head), request-major, each (request, head block) preceded by
+//    PIECE_COST places that stand for what a piece costs beside its tiles; block c owns the contiguous places
+//    [c * T / NB, (c + 1) * T / NB), so every SM has the same load whether the batch holds a few long requests,
+//    many short ones or both.  Entries that only fill a batch up to a fixed shape (their token has no page) take
+//    no place at all; their output rows are cleared.
 //  * A producer warp streams its block's tiles through a ring of shared-memory stages with TMA tile copies straight
 //    from the paged pool (the pool seen as one matrix [pages * 2 * kv_heads * page_size, D]; boxes of 64 columns x
 //    32 keys in the 128-byte swizzle; plain per-block copies, no multicast; completion counted in bytes on an
@@ -73,6 +76,13 @@ constexpr size_t smem_bytes(int stages, int mrows) { return 1024 + (size_t)stage
 static_assert(smem_bytes(STAGES_MIN, 16) + 8 * 1024 <= 227 * 1024 && smem_bytes(STAGES_DEEP, 8) + 8 * 1024 <= 227 * 1024,
               "ring, merge buffer and queries must fit one block's shared memory");
 constexpr int MIN_TILES = 4;
+// What a piece costs a block beside its tiles (the query heads' norm and rotation, the merge of the warps, the
+// output), in tiles' worth of time: the blocks' shares are equal in tiles + PIECE_COST per (request, head block),
+// so a block that gets many short requests gets fewer of them.
+#ifndef NHV_PIECE_COST
+#define NHV_PIECE_COST 8
+#endif
+constexpr int PIECE_COST = NHV_PIECE_COST;
 constexpr float LOG2E = 1.4426950408889634f;
 
 typedef __nv_bfloat16 bf16;
@@ -253,7 +263,8 @@ struct alignas(64) Params {
 
 struct Piece {
   int seq, hb, t_begin, n_tiles, nt;
-  long long first;          // first tile (in the flat list) of this piece's (request, head block)
+  int advance;              // how far the piece reaches along the blocks' common axis (tiles and piece costs)
+  long long first;          // where this piece's (request, head block) starts on that axis; its tiles follow PIECE_COST later
 };
 
 // STAGES: ring stages (a multiple of NCW); MROWS: rows of the merge buffer (16, or 8 for groups of up to 8 heads).
@@ -267,7 +278,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   float* mml = mo + NCW * MROWS * D;                                            // [NCW][MROWS][2]
   bf16* qbuf = reinterpret_cast<bf16*>(mml + NCW * MROWS * 2);                  // [16][D], chunks exchanged as in a tile
   __shared__ __align__(16) bf16 s_new[2][D];                  // the new token's key and value (fused form)
-  __shared__ unsigned short s_cnt[MAX_SEQS];                 // tiles of each request (0: not a single-token request)
+  __shared__ unsigned short s_cnt[MAX_SEQS];                 // tiles of each request (0: not a single-token request, or idle)
+  __shared__ unsigned char s_idle[MAX_SEQS];                 // 1: an idle entry (a single token whose newest key has no page)
   __shared__ int s_prefix[MAX_SEQS + 1];
   __shared__ uint64_t full[STAGES], empty[STAGES];
   __shared__ int s_tile_ok[STAGES];                          // 0: the tile's page is not there, nothing of it counts
@@ -296,20 +308,30 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   const int chunks = (G + 15) / 16;                          // groups of more than 16 heads: several head blocks
   const int H = nkv * chunks;                                // head blocks per request
   for (int sq = threadIdx.x; sq < n_seqs; sq += THREADS) {
-    int nt = 0;
+    int nt = 0, idle = 0;
     if (p.cu_q[sq + 1] - p.cu_q[sq] == 1) {
       const int total = p.kv_len[sq];
       const int lo = window > 0 ? max(0, total - window) : 0;
       nt = total > 0 ? (total - 1) / BN - lo / BN + 1 : 0;
+      // An entry that only fills the batch up to a fixed shape has no page for its token: it costs nothing here
+      // (no tiles, no piece) and its output rows are cleared.
+      const int newest = total > 0 ? __ldg(p.block_table + (size_t)sq * p.bt_stride + (total - 1) / page_size) : -1;
+      if (newest < 0 || newest >= p.n_pages) {
+        nt = 0;
+        idle = 1;
+      }
     }
     s_cnt[sq] = (unsigned short)min(nt, 65535);
+    s_idle[sq] = (unsigned char)idle;
   }
   __syncthreads();
+  // a request's share of the common axis: per head block its tiles and the cost of a piece
+  auto weight = [&](int sq) { return s_cnt[sq] ? (int)s_cnt[sq] + PIECE_COST : 0; };
   if (warp == 0) {                                           // prefix sums: each lane a run of requests, then a warp scan
     const int per = (n_seqs + 31) / 32;
     const int b0 = min(lane * per, n_seqs), b1 = min(b0 + per, n_seqs);
     int sum = 0;
-    for (int i = b0; i < b1; ++i) sum += s_cnt[i];
+    for (int i = b0; i < b1; ++i) sum += weight(i);
     int incl = sum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -317,7 +339,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       if (lane >= o) incl += v;
     }
     int run = incl - sum;
-    for (int i = b0; i < b1; ++i) { s_prefix[i] = run; run += s_cnt[i]; }
+    for (int i = b0; i < b1; ++i) { s_prefix[i] = run; run += weight(i); }
     if (lane == 31) s_prefix[n_seqs] = incl;
   }
   __syncthreads();
@@ -326,7 +348,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   // owners of consecutive tiles are consecutive blocks and a request is cut into few pieces
   const int NB = (int)max(1LL, min((long long)gridDim.x, T / MIN_TILES));
   const int c = blockIdx.x;
-  if (c >= NB || T == 0) return;
+  // idle entries' output rows, dealt to the blocks; after the wait for the predecessor, which may still read them
+  auto clear_idle_rows = [&](int tid, int n_threads) {
+    for (int sq = c; sq < n_seqs; sq += gridDim.x) {
+      if (!s_idle[sq]) continue;
+      bf16* dst = p.out + (size_t)p.cu_q[sq] * p.out_stride;
+      for (int id = tid; id < p.nq * CH; id += n_threads) reinterpret_cast<uint4*>(dst)[id] = make_uint4(0, 0, 0, 0);
+    }
+  };
+  if (c >= NB || T == 0) {
+    if (early) pdl_wait();
+    clear_idle_rows(threadIdx.x, THREADS);
+    return;
+  }
   const long long u0 = (long long)c * T / NB, u1 = (long long)(c + 1) * T / NB;
 
   // which request, head block and tiles does the piece that starts at u hold?
@@ -339,11 +373,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     Piece pc;
     pc.seq = lo_s;
     pc.nt = s_cnt[pc.seq];
+    const int w = pc.nt + PIECE_COST;                        // the span of one (request, head block): the cost, then its tiles
     const long long seq_base = (long long)H * s_prefix[pc.seq];
-    pc.hb = (int)((u - seq_base) / pc.nt);
-    pc.t_begin = (int)((u - seq_base) - (long long)pc.hb * pc.nt);
-    pc.first = seq_base + (long long)pc.hb * pc.nt;
-    pc.n_tiles = (int)(min(u1, pc.first + pc.nt) - u);
+    pc.hb = (int)((u - seq_base) / w);
+    pc.first = seq_base + (long long)pc.hb * w;
+    const int x0 = (int)(u - pc.first), x1 = (int)(min(u1, pc.first + w) - pc.first);
+    pc.advance = x1 - x0;
+    pc.t_begin = max(0, x0 - PIECE_COST);
+    pc.n_tiles = max(0, x1 - PIECE_COST) - pc.t_begin;      // 0: the block's range ends before this one's first tile
     return pc;
   };
 
@@ -353,7 +390,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     int ok = 1;
     for (long long u = u0; u < u1 && ok;) {
       const Piece pc = piece_at(u);
-      u += pc.n_tiles;
+      u += pc.advance;
+      if (pc.n_tiles == 0) continue;
       const int kvh = pc.hb / chunks;
       const int total = p.kv_len[pc.seq];
       const int lo = window > 0 ? max(0, total - window) : 0;
@@ -400,8 +438,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   uint32_t gi_base = 0;
   for (long long u = u0; u < u1;) {
     const Piece pc = piece_at(u);
-    const bool starts_range = u == u0;
-    u += pc.n_tiles;
+    u += pc.advance;
+    if (pc.n_tiles == 0) continue;
     const int seq = pc.seq, hb = pc.hb, n_tiles = pc.n_tiles, nt = pc.nt;
     const bool whole = pc.t_begin == 0 && n_tiles == nt;
     const int kvh = hb / chunks, g0 = (hb - kvh * chunks) * 16;
@@ -537,8 +575,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     }
     consumer_sync();
     const size_t unit = (size_t)seq * H + hb;                  // this (request, head block)
-    // a block has at most two pieces that are not whole: the one at the start of its range and the one at its end
-    const int slot = starts_range ? 0 : 1;
+    // a block has at most two pieces that are not whole: one that goes on where the block before it stopped (only
+    // at the start of its range) and one that its range's end cuts short (only at that end)
+    const int slot = pc.t_begin > 0 ? 0 : 1;
     float* po = p.part_o + ((size_t)c * 2 + slot) * 16 * D;
     float* pml = p.part_ml + ((size_t)c * 2 + slot) * 16 * 2;
     for (int id = threadIdx.x; id < gn * (D / 4); id += NCW * 32) {
@@ -575,12 +614,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
         s_flag = old;
       }
       consumer_sync();
-      const int first_owner = tile_owner(pc.first, T, NB);
-      const int pieces = tile_owner(pc.first + nt - 1, T, NB) - first_owner + 1;
+      const int first_owner = tile_owner(pc.first + PIECE_COST, T, NB);
+      const int pieces = tile_owner(pc.first + PIECE_COST + nt - 1, T, NB) - first_owner + 1;
       if (s_flag == pieces - 1) {                              // the last piece to arrive: merge all, in block order
-        // the first owner's piece lies at the end of its range unless its range starts with this (request, head
-        // block); every other owner's piece lies at the start of its range
-        const int first_slot = (long long)first_owner * T / NB < pc.first ? 1 : 0;
+        // the first owner's piece starts with the first tile (slot 1); every other owner's goes on from the block
+        // before it (slot 0)
+        constexpr int first_slot = 1;
         for (int id = threadIdx.x; id < gn * (D / 4); id += NCW * 32) {
           const int R = id / (D / 4), c4 = id - R * (D / 4);
           float M = -INFINITY;
@@ -618,6 +657,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     }
     consumer_sync();                                           // the merge buffers and the query are reused by the next piece
   }
+  if (!waited) pdl_wait();
+  clear_idle_rows(threadIdx.x, NCW * 32);
   if (!ok) give_up_delay();
 }
 

@@ -243,9 +243,10 @@ def attention_tcgen05_error(head_dim: int) -> int:
 def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_prefill_tokens: int,
                           n_prefill_seqs: int, n_decode_seqs: int, max_kv_len: int, nq: int, nkv: int, head_dim: int,
                           scale: float, window: int = 0) -> None:
-    """bfloat16 attention on the tensor cores.  Requests with one new token go through the split
-    kernel and its merge (scratch: one partial result per request, head and split of 256 keys); the
-    others through the prompt kernel."""
+    """bfloat16 attention on the tensor cores.  Prompt portions go to the tcgen05 kernel, requests with
+    one new token to the kernel that streams the cache with TMA, each where its shape is supported; what
+    neither takes runs in the mma.sync kernel, whose single-token path shares a request's tiles between
+    blocks and merges them (scratch: one partial result per piece of a request and head block)."""
     _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len)
     _contig("kv_pages", kv_pages)
     assert q.dtype == out.dtype == kv_pages.dtype == torch.bfloat16 and q.stride(-1) == 1 and out.stride(-1) == 1

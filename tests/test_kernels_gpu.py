@@ -515,7 +515,8 @@ def test_sampler_follows_the_distribution(ops):
 def test_attention_decode_many_requests_through_the_tma_ring(ops, nq, nkv, d, page, window):
     """Forty single-token requests of 1 to 3,000 keys: every block of the persistent decode kernel walks many
     tiles, whole requests and the ends of requests that it shares with its neighbours, and the ring is reused
-    many times over; against the float64 reference, with NaN wherever no key lies."""
+    many times over; against the float64 reference, with NaN wherever no key lies.  Among and behind them idle
+    entries as a padded batch has them (one token, no page): their rows come back cleared."""
     from nanohybrid_vlm_b200.kernels import attention_decode
     assert attention_decode.supports(d, nq, nkv, page)
     rng = np.random.default_rng(5)
@@ -546,6 +547,12 @@ def test_attention_decode_many_requests_through_the_tma_ring(ops, nq, nkv, d, pa
         tables.append(ids)
         qs.append(q)
         refs.append(reference_attention(q, k, v, scale, window))
+    for at in (4, 21, S + 2, S + 3, S + 4, S + 5, S + 6):    # idle entries
+        lens.insert(at, 1)
+        tables.insert(at, [])
+        qs.insert(at, torch.randn(1, nq, d, generator=g).to(torch.bfloat16))
+        refs.insert(at, torch.zeros(1, nq, d))
+    S = len(lens)
     width = max(len(t) for t in tables)
     bt = torch.full((S, width), -1, dtype=torch.int32)
     for i, t in enumerate(tables):
