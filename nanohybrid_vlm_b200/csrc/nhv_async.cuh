@@ -53,6 +53,11 @@ static __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap*
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+// The same of a 4-D tensor map (x innermost).
+static __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int x, int y, int z, int w, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+               ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar)) : "memory");
+}
 // A linear copy: both addresses 16-byte aligned, the size a multiple of 16 bytes.
 static __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
@@ -77,6 +82,33 @@ static inline void* nhv_wait_error_address() {
   void* p = nullptr;
   if (cudaGetSymbolAddress(&p, g_wait_error) != cudaSuccess) return nullptr;
   return p;
+}
+
+// A tensor map of `rank` (2 to 5) dimensions over bfloat16 elements, innermost first: dims[i] elements that lie
+// stride_bytes[i] apart (stride_bytes[0] is 2 and is not passed on; the others must be multiples of 16 and need
+// not grow with i), read in boxes of box[i] with the 128-byte swizzle (box[0] * 2 bytes must not exceed 128).  A
+// box arrives in shared memory with dimension 0 fastest, then 1, 2, ...
+static inline bool nhv_make_map_bf16_nd(CUtensorMap* map, const void* base, int rank, const long long* dims,
+                                        const long long* stride_bytes, const int* box) {
+  static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
+    encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+  }
+  if (rank < 2 || rank > 5) return false;
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = (cuuint64_t)dims[i];
+    bx[i] = (cuuint32_t)box[i];
+    es[i] = 1;
+    if (i > 0) st[i - 1] = (cuuint64_t)stride_bytes[i];
+  }
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, st, bx, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // A tensor map over a row-major bfloat16 matrix [rows, cols] whose rows lie `row_stride_elems` apart, read in

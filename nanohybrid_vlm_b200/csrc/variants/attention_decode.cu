@@ -246,7 +246,7 @@ __device__ __forceinline__ void warp_half_tile(RowState& st, const uint32_t (&qf
 }
 
 struct alignas(64) Params {
-  CUtensorMap pool_map;     // the pool as [pages * 2 * nkv * page_size, D], box 64 columns x 64 rows
+  CUtensorMap pool_map;     // the pool in four dimensions: one box is a tile's keys and values (see where it is made)
   const bf16* q;            // plain form: [tokens, nq * D]
   bf16* out;
   bf16* kv_pages;
@@ -409,22 +409,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
         const int n_here = min(32, pc.n_tiles - it0);
         for (int j = 0; j < n_here; ++j) {
           const int rk = __shfl_sync(0xffffffffu, row, j), th = __shfl_sync(0xffffffffu, there, j);
+          const int stage = gi % STAGES;
           if (lane == 0) {
-            const int stage = gi % STAGES;
             if (gi >= (uint32_t)STAGES) ok = mbar_wait(&empty[stage], ((gi / STAGES) - 1) & 1, 1) ? 1 : 0;
             if (ok) {
               s_tile_ok[stage] = th;
               mbar_expect_tx(&full[stage], STAGE_BYTES);
-              unsigned char* dst = ring + (size_t)stage * STAGE_BYTES;
-              const int rv = rk + nkv * page_size;           // the page's values follow its keys
-#pragma unroll
-              for (int b = 0; b < DB; ++b) tma_load_2d(dst + b * BN * 128, &p.pool_map, b * 64, rk, &full[stage]);
-#pragma unroll
-              for (int b = 0; b < DB; ++b) tma_load_2d(dst + TILE_BYTES + b * BN * 128, &p.pool_map, b * 64, rv, &full[stage]);
             }
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
+          // the whole tile in one copy: the box holds 64 columns x the tile's keys x the head's column blocks x
+          // (keys, values), and arrives in that order (a copy costs the TMA unit about as much whatever it holds)
+          if (lane == 0) tma_load_4d(ring + (size_t)stage * STAGE_BYTES, &p.pool_map, 0, rk, 0, 0, &full[stage]);
           ++gi;
         }
       }
@@ -715,8 +712,8 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
               "attention (decode, TMA): pages must be a multiple of %d keys, got %d", BN, page_size);
   ATT_REQUIRE(n_seqs > 0 && n_seqs <= MAX_SEQS, "attention: %d requests in a step, the decode kernel plans for up to %d", n_seqs, MAX_SEQS);
   ATT_REQUIRE(part_o && part_ml && counters, "attention: decoding needs scratch memory for the pieces of split requests");
-  ATT_REQUIRE(out_stride % 4 == 0 && ((uintptr_t)out % 8) == 0 && ((uintptr_t)kv_pages % 16) == 0,
-              "attention: the pages must be 16-byte aligned, the output 8-byte aligned");
+  ATT_REQUIRE(out_stride % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)kv_pages % 16) == 0,
+              "attention: the pages, the output and the output's rows must be 16-byte aligned");
   ATT_REQUIRE((long long)n_pages * 2 * nkv * page_size < (1LL << 31), "attention: the pool has more rows than a tensor map's 32-bit coordinate");
   Params p;
   p.fq = FusedQK{};
@@ -748,7 +745,13 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
     auto it = maps.find(kv_pages);
     if (it == maps.end() || it->second.first != rows) {
       CUtensorMap m;
-      ATT_REQUIRE(nhv_make_map_bf16(&m, kv_pages, rows, D, D, 64, BN), "attention (decode, TMA): cannot encode the tensor map of the pool");
+      // the pool as [keys or values of a page][column block of 64][row of the pool][64 columns]: the values of a
+      // (page, KV head) lie nkv * page_size rows behind its keys
+      const long long half = (long long)nkv * page_size;
+      const long long dims[4] = {64, rows - half, DB, 2};
+      const long long strides[4] = {2, (long long)D * 2, 128, half * D * 2};
+      const int box[4] = {64, BN, DB, 2};
+      ATT_REQUIRE(nhv_make_map_bf16_nd(&m, kv_pages, 4, dims, strides, box), "attention (decode, TMA): cannot encode the tensor map of the pool");
       maps[kv_pages] = {rows, m};
       it = maps.find(kv_pages);
     }
