@@ -11,7 +11,8 @@
 // box of 64 columns; in a box rows of 128 bytes, mode 2: the gate rows then the up rows; the 16-byte chunks of
 // row r exchanged by c ^ (r & 7), which is what ldmatrix reads without bank conflicts), so a stage arrives by
 // one linear bulk copy of up to 32 KB (cp.async.bulk, completion counted in bytes on an mbarrier).  x comes by TMA
-// tensor copies with the same swizzle.
+// tensor copies with the same swizzle: a stage's columns in one copy where K is a multiple of 64 (x seen as
+// [K / 64][M][64]), since what the TMA unit can take is a number of copies rather than of bytes.
 //
 // One producer thread streams the stages through a ring; four consumer warps take a quarter of each stage's
 // columns each (mma.sync.m16n8k16, W rows on the MMA's M axis, tokens on its N axis, fp32 accumulators) and add
@@ -58,7 +59,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 struct alignas(64) Params {
-  CUtensorMap x_map;     // x [M, K], box 64 columns x 8 rows
+  CUtensorMap x_map;     // x [M, K]: x3d: as [K / 64][M][64], one box is a stage's columns; else box 64 columns x 8 rows
   const unsigned char* slabs;
   void* y;
   long long slab_bytes;  // one block's share
@@ -66,6 +67,7 @@ struct alignas(64) Params {
   int rpb;               // result columns per block
   int nb;                // boxes of 64 columns per stage
   int ks;                // stages over K (K padded to ks * nb * 64 columns in the copy)
+  int x3d;               // K is a multiple of 64: a stage's columns of x come in one copy
 };
 
 __global__ void __launch_bounds__(THREADS, 1) gemm_slab_kernel(const __grid_constant__ Params p) {
@@ -112,7 +114,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_slab_kernel(const __grid_cons
         const int k = i % p.ks;
         const int s = i % STAGES;
         unsigned char* dst = ring + (size_t)s * STAGE_BYTES + W_STAGE_BYTES;
-        for (int b = 0; b < p.nb; ++b) tma_load_2d(dst + b * X_BOX_BYTES, &p.x_map, (k * p.nb + b) * 64, 0, &full[s]);
+        // one copy where it can be (a copy costs the TMA unit about as much whatever it holds): the box holds the
+        // stage's nb column blocks one after the other, as the separate copies lay them
+        if (p.x3d) {
+          tma_load_3d(dst, &p.x_map, 0, 0, k * p.nb, &full[s]);
+        } else {
+          for (int b = 0; b < p.nb; ++b) tma_load_2d(dst + b * X_BOX_BYTES, &p.x_map, (k * p.nb + b) * 64, 0, &full[s]);
+        }
       };
       // Fill the ring with weights while the kernel before this one may still be running, then wait for it.
       const int pre = min(STAGES, units);
@@ -218,6 +226,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_slab_kernel(const __grid_cons
 bool make_x_map(CUtensorMap* map, const void* base, int rows, int cols, int row_stride_elems) {
   return nhv_make_map_bf16(map, base, rows, cols, row_stride_elems, 64, X_ROWS);
 }
+// x as [cols / 64][rows][64] (cols a multiple of 64): a box of nb column blocks; blocks beyond the last read as zero
+bool make_x_map_3d(CUtensorMap* map, const void* base, int rows, int cols, int row_stride_elems, int nb) {
+  const long long dims[3] = {64, rows, cols / 64};
+  const long long strides[3] = {2, (long long)row_stride_elems * 2, 128};
+  const int box[3] = {64, X_ROWS, nb};
+  return nhv_make_map_bf16_nd(map, base, 3, dims, strides, box);
+}
 
 }  // namespace
 
@@ -264,7 +279,9 @@ NHV_API int nhv_gemm_slab(void* y, const void* x, const void* slabs, int M, int 
   p.slabs = (const unsigned char*)slabs;
   p.y = y;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.mode = mode;
-  NHV_REQUIRE(make_x_map(&p.x_map, x, M, K, lda), "gemm_slab: cannot encode the tensor map of x [%d, %d]", M, K);
+  p.x3d = K % 64 == 0;
+  NHV_REQUIRE(p.x3d ? make_x_map_3d(&p.x_map, x, M, K, lda, p.nb) : make_x_map(&p.x_map, x, M, K, lda),
+              "gemm_slab: cannot encode the tensor map of x [%d, %d]", M, K);
   constexpr size_t smem = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)CONSUMER_WARPS * ROWS * X_ROWS * 4 + 2 * STAGES * 8;
   static_assert(smem <= 227 * 1024, "the ring and the reduction buffer must fit one block's shared memory");
   static bool attr_set = false;

@@ -148,11 +148,13 @@ def test_gemm_small_m(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 5, 8])
-@pytest.mark.parametrize("N,K", [(384, 96), (1000, 264), (4096, 4096), (24578, 520), (50, 12288), (7, 40), (6144, 4096)])
+@pytest.mark.parametrize("N,K", [(384, 96), (1000, 264), (4096, 4096), (24578, 520), (50, 12288), (7, 40), (6144, 4096),
+                                 (384, 192), (1000, 320)])
 def test_gemm_from_slabs(ops, M, N, K):
     """The decode step's products from the copy of the weights that is cut into one share of rows per SM
     (csrc/gemm_slab.cu): plain, float32 output and the fused SwiGLU half, against fp64; shapes whose shares are 1,
-    3, 7, 28, 42 and 167 rows, whose columns need padding to the stage, and whose last share is short; and what
+    3, 7, 28, 42 and 167 rows, whose columns need padding to the stage (with K a multiple of 64, where a stage's
+    columns of x come in one copy, and not), and whose last share is short; and what
     ``ops.linear`` takes by itself once ``prepare_streaming`` has registered the copy."""
     g = torch.Generator().manual_seed(31)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
