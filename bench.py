@@ -152,7 +152,8 @@ def bench_ours(args) -> dict:
         pages = max_b * (CONTEXT // PAGE) + 2 * (CONTEXT // PAGE)
         llm = LLM(d, random_weights_seed=SEED, kvcache_block_size=PAGE, num_kvcache_blocks=pages,
                   max_model_len=CONTEXT, max_num_seqs=max_b, max_num_batched_tokens=8192, seed=SEED,
-                  enforce_eager=args.eager, async_decode=not args.sync)
+                  enforce_eager=args.eager, async_decode=not args.sync,
+                  decode_weight_copy=False if args.no_weight_copy else None)
     runner = llm.model_runner
     params = SamplingParams(temperature=0.0, max_tokens=CONTEXT - PROMPT_LEN, ignore_eos=True)
 
@@ -654,6 +655,8 @@ def main() -> int:
     ap.add_argument("--workload", default="8b", choices=["8b", "0.6b", "32b"],
                     help="8b: the headline line; 0.6b / 32b: the baseline's other workloads through LLM.add_request / step")
     ap.add_argument("--sync", action="store_true", help="read every decode step's tokens before the next is launched (async_decode off)")
+    ap.add_argument("--no-weight-copy", action="store_true",
+                    help="decode from the row-major matrices (no per-SM copies of the weights: half the weight memory)")
     ap.add_argument("--requests", type=int, default=0, help="fewer requests than the workload names (trying it out)")
     ap.add_argument("--breakdown", action="store_true",
                     help="time by kind of kernel in an eager run with --layers layers (default 2); prints one JSON line")
