@@ -12,15 +12,19 @@
 //    many short ones or both.  Entries that only fill a batch up to a fixed shape (their token has no page) take
 //    no place at all; their output rows are cleared.
 //  * A producer warp streams its block's tiles through a ring of shared-memory stages with TMA tile copies straight
-//    from the paged pool (the pool seen as one matrix [pages * 2 * kv_heads * page_size, D]; boxes of 64 columns x
-//    32 keys in the 128-byte swizzle; plain per-block copies, no multicast; completion counted in bytes on an
-//    mbarrier).  It looks the pages of 32 tiles up at a time and runs ahead of the consumers across the borders of
-//    requests, so the ring never drains: up to 12 stages of 2 * 32 * D * 2 bytes
-//    (192 KB at head size 128) are in flight per SM.
+//    from the paged pool, a tile's keys and values in ONE copy: the pool is seen in four dimensions, [keys | values]
+//    [column block of 64][row of the pool][64 columns], and a box of 2 x D/64 x 32 x 64 lands as the K tile followed
+//    by the V tile, each column block by column block in the 128-byte swizzle (64 columns is the widest box that
+//    swizzle takes, and what an SM's TMA unit can take is about nine copies a microsecond whatever they hold: with
+//    a copy per 64-column block of K and of V the launch was bound by copies, not bytes).  Plain per-block copies,
+//    no multicast; completion counted in bytes on an mbarrier.  The producer looks the pages of 32 tiles up at a
+//    time and runs ahead of the consumers across the borders of requests, so the ring never drains: up to 12
+//    stages of 2 * 32 * D * 2 bytes (192 KB at head size 128) are in flight per SM.
 //  * The consumer warps (four for head sizes up to 128) take whole tiles in turn (tile t of the block goes to warp
-//    t % NCW): no warp waits for another while a piece lasts.  mma.sync.m16n8k16 bf16 with fp32 accumulation, online softmax in fp32 on base-2
-//    exponents, the rows being the query heads of the group (padded to 16).  At the end of a piece (a block's tiles
-//    of one (request, head block)) the four warps' states are merged through shared memory.
+//    t % NCW): no warp waits for another while a piece lasts.  mma.sync.m16n8k16 bf16 with fp32 accumulation, online
+//    softmax in fp32 on base-2 exponents, the rows being the query heads of the group (padded to 16).  At the end
+//    of a piece (a block's tiles of one (request, head block)) the four warps' states are merged through shared
+//    memory.
 //  * If a piece is the whole of its (request, head block) the block writes the output; otherwise it stores (max,
 //    sum, unnormalised output) to scratch (a block has at most two such pieces: its first and its last), and the
 //    block that arrives last at that (request, head block)'s counter merges all pieces in block order and writes
