@@ -77,7 +77,7 @@ constexpr int Q_BYTES = 16 * D * 2;
 constexpr int merge_bytes(int mrows) { return NCW * mrows * D * 4 + NCW * mrows * 2 * 4; }
 constexpr int MAX_SEQS = 512;
 constexpr size_t smem_bytes(int stages, int mrows) { return 1024 + (size_t)stages * STAGE_BYTES + merge_bytes(mrows) + Q_BYTES; }
-static_assert(smem_bytes(STAGES_MIN, 16) + 8 * 1024 <= 227 * 1024 && smem_bytes(STAGES_DEEP, 8) + 8 * 1024 <= 227 * 1024,
+static_assert(smem_bytes(STAGES_MIN, 16) + 9 * 1024 <= 227 * 1024 && smem_bytes(STAGES_DEEP, 8) + 9 * 1024 <= 227 * 1024,
               "ring, merge buffer and queries must fit one block's shared memory");
 constexpr int MIN_TILES = 4;
 // What a piece costs a block beside its tiles (the query heads' norm and rotation, the merge of the warps, the
@@ -133,11 +133,16 @@ struct FusedQK {
 
 constexpr int FVEC = D / 32;                                 // elements of a head per lane
 
-// One head of the new token in this warp: lane l gets elements [l * FVEC, (l + 1) * FVEC).
-__device__ __forceinline__ void fused_head(float (&v)[FVEC], const bf16* src, const bf16* w, const float* cs,
-                                           const FusedQK& f, int lane) {
+// One head of the new token in this warp: lane l gets elements [l * FVEC, (l + 1) * FVEC).  The load (one access
+// of FVEC * 2 bytes) and what follows it (norm, rotation) apart, so that a second head's load can be on its way
+// before the first head's is used.
+struct alignas((FVEC * 2) & -(FVEC * 2)) HeadChunk { bf16 e[FVEC]; };   // 4, 8, 4 (head size 192) or 16 bytes
+__device__ __forceinline__ void head_load(float (&v)[FVEC], const bf16* src, int lane) {
+  const HeadChunk c = *reinterpret_cast<const HeadChunk*>(src + lane * FVEC);
 #pragma unroll
-  for (int k = 0; k < FVEC; ++k) v[k] = __bfloat162float(src[lane * FVEC + k]);
+  for (int k = 0; k < FVEC; ++k) v[k] = __bfloat162float(c.e[k]);
+}
+__device__ __forceinline__ void head_finish(float (&v)[FVEC], const bf16* w, const float* cs, const FusedQK& f, int lane) {
   if (w) {
     float ss = 0.f;
 #pragma unroll
@@ -165,6 +170,11 @@ __device__ __forceinline__ void fused_head(float (&v)[FVEC], const bf16* src, co
       }
     }
   }
+}
+__device__ __forceinline__ void fused_head(float (&v)[FVEC], const bf16* src, const bf16* w, const float* cs,
+                                           const FusedQK& f, int lane) {
+  head_load(v, src, lane);
+  head_finish(v, w, cs, f, lane);
 }
 
 // Running softmax state of the two rows (lane/4 and lane/4 + 8) a thread holds of the 16 rows.
@@ -285,6 +295,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   __shared__ unsigned short s_cnt[MAX_SEQS];                 // tiles of each request (0: not a single-token request, or idle)
   __shared__ unsigned char s_idle[MAX_SEQS];                 // 1: an idle entry (a single token whose newest key has no page)
   __shared__ int s_prefix[MAX_SEQS + 1];
+  __shared__ int s_total[MAX_SEQS];                          // keys of each request, its new one included
+  __shared__ int s_tok[MAX_SEQS];                            // row of each request's token in q / qkv / out
   __shared__ uint64_t full[STAGES], empty[STAGES];
   __shared__ int s_tile_ok[STAGES];                          // 0: the tile's page is not there, nothing of it counts
   __shared__ int s_flag;
@@ -327,6 +339,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     }
     s_cnt[sq] = (unsigned short)min(nt, 65535);
     s_idle[sq] = (unsigned char)idle;
+    s_total[sq] = p.kv_len[sq];
+    s_tok[sq] = p.cu_q[sq];
   }
   __syncthreads();
   // a request's share of the common axis: per head block its tiles and the cost of a piece
@@ -356,7 +370,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   auto clear_idle_rows = [&](int tid, int n_threads) {
     for (int sq = c; sq < n_seqs; sq += gridDim.x) {
       if (!s_idle[sq]) continue;
-      bf16* dst = p.out + (size_t)p.cu_q[sq] * p.out_stride;
+      bf16* dst = p.out + (size_t)s_tok[sq] * p.out_stride;
       for (int id = tid; id < p.nq * CH; id += n_threads) reinterpret_cast<uint4*>(dst)[id] = make_uint4(0, 0, 0, 0);
     }
   };
@@ -367,24 +381,48 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   }
   const long long u0 = (long long)c * T / NB, u1 = (long long)(c + 1) * T / NB;
 
-  // which request, head block and tiles does the piece that starts at u hold?
-  auto piece_at = [&](long long u) {
+  // A walk along the block's range, one (request, head block) after the other: `first` is where the span of the
+  // current one starts (its cost, then its tiles).  Found once by search, then stepped: a piece costs no search
+  // and no 64-bit division.
+  struct Cursor {
+    int seq, hb;
+    long long first;
+  };
+  auto cursor_at = [&](long long u) {
     int lo_s = 0, hi_s = n_seqs;
     while (lo_s < hi_s) {
       const int mid = (lo_s + hi_s) >> 1;
       if ((long long)H * s_prefix[mid + 1] > u) hi_s = mid; else lo_s = mid + 1;
     }
+    Cursor cu;
+    cu.seq = lo_s;
+    const int w = (int)s_cnt[cu.seq] + PIECE_COST;
+    const long long seq_base = (long long)H * s_prefix[cu.seq];
+    cu.hb = (int)(u - seq_base) / w;                         // at most H * w places: 32 bits do
+    cu.first = seq_base + (long long)cu.hb * w;
+    return cu;
+  };
+  // the piece of the cursor's (request, head block) that starts at place u and ends with it or with the block's
+  // range; moves u behind the piece and the cursor on if the (request, head block) ends there
+  auto next_piece = [&](Cursor& cu, long long& u) {
     Piece pc;
-    pc.seq = lo_s;
-    pc.nt = s_cnt[pc.seq];
+    pc.seq = cu.seq;
+    pc.hb = cu.hb;
+    pc.first = cu.first;
+    pc.nt = s_cnt[cu.seq];
     const int w = pc.nt + PIECE_COST;                        // the span of one (request, head block): the cost, then its tiles
-    const long long seq_base = (long long)H * s_prefix[pc.seq];
-    pc.hb = (int)((u - seq_base) / w);
-    pc.first = seq_base + (long long)pc.hb * w;
-    const int x0 = (int)(u - pc.first), x1 = (int)(min(u1, pc.first + w) - pc.first);
+    const int x0 = (int)(u - cu.first), x1 = (int)(min(u1, cu.first + w) - cu.first);
     pc.advance = x1 - x0;
     pc.t_begin = max(0, x0 - PIECE_COST);
     pc.n_tiles = max(0, x1 - PIECE_COST) - pc.t_begin;      // 0: the block's range ends before this one's first tile
+    u += pc.advance;
+    if (x1 == w) {                                           // on to the next (request, head block) that has tiles
+      cu.first += w;
+      if (++cu.hb == H) {
+        cu.hb = 0;
+        do ++cu.seq; while (cu.seq < n_seqs && s_cnt[cu.seq] == 0);
+      }
+    }
     return pc;
   };
 
@@ -392,12 +430,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     // ---------------------------------------------------------------- producer
     uint32_t gi = 0;                                         // tiles sent so far: stage gi % STAGES
     int ok = 1;
+    Cursor cur = cursor_at(u0);
     for (long long u = u0; u < u1 && ok;) {
-      const Piece pc = piece_at(u);
-      u += pc.advance;
+      const Piece pc = next_piece(cur, u);
       if (pc.n_tiles == 0) continue;
       const int kvh = pc.hb / chunks;
-      const int total = p.kv_len[pc.seq];
+      const int total = s_total[pc.seq];
       const int lo = window > 0 ? max(0, total - window) : 0;
       const int key_begin = (lo / BN + pc.t_begin) * BN;
       const int* table = p.block_table + (size_t)pc.seq * p.bt_stride;
@@ -437,18 +475,18 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   // ------------------------------------------------------------------ consumers
   bool waited = !early, ok = true;
   uint32_t gi_base = 0;
+  Cursor cur = cursor_at(u0);
   for (long long u = u0; u < u1;) {
-    const Piece pc = piece_at(u);
-    u += pc.advance;
+    const Piece pc = next_piece(cur, u);
     if (pc.n_tiles == 0) continue;
     const int seq = pc.seq, hb = pc.hb, n_tiles = pc.n_tiles, nt = pc.nt;
     const bool whole = pc.t_begin == 0 && n_tiles == nt;
     const int kvh = hb / chunks, g0 = (hb - kvh * chunks) * 16;
     const int gn = min(rows_per, G - g0);
-    const int total = p.kv_len[seq];
+    const int total = s_total[seq];
     const int lo = window > 0 ? max(0, total - window) : 0;
     const int key_begin = (lo / BN + pc.t_begin) * BN;
-    const size_t tok = p.cu_q[seq];
+    const size_t tok = s_tok[seq];
     const bool has_last = pc.t_begin + n_tiles == nt;         // this piece ends with the request's newest key
     if (!waited) {
       pdl_wait();
@@ -469,6 +507,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
         pos = pos < 0 ? 0 : (pos >= fq.max_position ? fq.max_position - 1 : pos);
         cs = fq.cos_sin + (size_t)pos * fq.rotary_dim;
       }
+      // warp 0: the new key, warp 1: the new value; asked for before the query heads, used behind them
+      const bool has_new = has_last && fq.store && warp < 2;
+      float nv[FVEC];
+      if (has_new) head_load(nv, row + (size_t)(p.nq + (warp == 0 ? 0 : nkv) + kvh) * D, lane);
       for (int R = warp; R < 16; R += NCW) {                  // the query heads of the group dealt to the warps
         float v[FVEC];
         if (R < gn) {
@@ -482,12 +524,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
         for (int k = 0; k < FVEC; ++k)      // a lane's elements may straddle two 16-byte chunks (head size 192)
           qbuf[tile_off<16>(R, (e0 + k) >> 3) + ((e0 + k) & 7)] = __float2bfloat16_rn(v[k]);
       }
-      if (has_last && fq.store && warp < 2) {                 // warp 0: the new key; warp 1: the new value
-        float v[FVEC];
-        const bf16* src = row + (size_t)(p.nq + (warp == 0 ? 0 : nkv) + kvh) * D;
-        fused_head(v, src, warp == 0 ? fq.k_w : nullptr, warp == 0 ? cs : nullptr, fq, lane);
+      if (has_new) {
+        head_finish(nv, warp == 0 ? fq.k_w : nullptr, warp == 0 ? cs : nullptr, fq, lane);
 #pragma unroll
-        for (int k = 0; k < FVEC; ++k) s_new[warp][lane * FVEC + k] = __float2bfloat16_rn(v[k]);
+        for (int k = 0; k < FVEC; ++k) s_new[warp][lane * FVEC + k] = __float2bfloat16_rn(nv[k]);
       }
     }
     consumer_sync();
