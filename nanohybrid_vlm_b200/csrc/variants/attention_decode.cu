@@ -77,7 +77,7 @@ constexpr int Q_BYTES = 16 * D * 2;
 constexpr int merge_bytes(int mrows) { return NCW * mrows * D * 4 + NCW * mrows * 2 * 4; }
 constexpr int MAX_SEQS = 512;
 constexpr size_t smem_bytes(int stages, int mrows) { return 1024 + (size_t)stages * STAGE_BYTES + merge_bytes(mrows) + Q_BYTES; }
-static_assert(smem_bytes(STAGES_MIN, 16) + 9 * 1024 <= 227 * 1024 && smem_bytes(STAGES_DEEP, 8) + 9 * 1024 <= 227 * 1024,
+static_assert(smem_bytes(STAGES_MIN, 16) + 11 * 1024 <= 227 * 1024 && smem_bytes(STAGES_DEEP, 8) + 11 * 1024 <= 227 * 1024,
               "ring, merge buffer and queries must fit one block's shared memory");
 constexpr int MIN_TILES = 4;
 // What a piece costs a block beside its tiles (the query heads' norm and rotation, the merge of the warps, the
@@ -297,6 +297,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   __shared__ int s_prefix[MAX_SEQS + 1];
   __shared__ int s_total[MAX_SEQS];                          // keys of each request, its new one included
   __shared__ int s_tok[MAX_SEQS];                            // row of each request's token in q / qkv / out
+  __shared__ int s_pos[MAX_SEQS];                            // fused form with rotation: the token's position, clamped
   __shared__ uint64_t full[STAGES], empty[STAGES];
   __shared__ int s_tile_ok[STAGES];                          // 0: the tile's page is not there, nothing of it counts
   __shared__ int s_flag;
@@ -324,14 +325,21 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   const int chunks = (G + 15) / 16;                          // groups of more than 16 heads: several head blocks
   const int H = nkv * chunks;                                // head blocks per request
   for (int sq = threadIdx.x; sq < n_seqs; sq += THREADS) {
+    // three loads at once, then the two that need their answers (also at once); all of them are the step's input,
+    // which no kernel before this one writes
+    const int tok = __ldg(p.cu_q + sq), tok_end = __ldg(p.cu_q + sq + 1), total = __ldg(p.kv_len + sq);
+    const bool single = tok_end - tok == 1;
+    const int newest = single && total > 0 ? __ldg(p.block_table + (size_t)sq * p.bt_stride + (total - 1) / page_size) : -1;
+    if (fused && fq.cos_sin) {                               // so that no piece waits for its position before it can ask for its cosines
+      const int pos = single ? __ldg(fq.positions + tok) : 0;
+      s_pos[sq] = pos < 0 ? 0 : (pos >= fq.max_position ? fq.max_position - 1 : pos);
+    }
     int nt = 0, idle = 0;
-    if (p.cu_q[sq + 1] - p.cu_q[sq] == 1) {
-      const int total = p.kv_len[sq];
+    if (single) {
       const int lo = window > 0 ? max(0, total - window) : 0;
       nt = total > 0 ? (total - 1) / BN - lo / BN + 1 : 0;
       // An entry that only fills the batch up to a fixed shape has no page for its token: it costs nothing here
       // (no tiles, no piece) and its output rows are cleared.
-      const int newest = total > 0 ? __ldg(p.block_table + (size_t)sq * p.bt_stride + (total - 1) / page_size) : -1;
       if (newest < 0 || newest >= p.n_pages) {
         nt = 0;
         idle = 1;
@@ -339,8 +347,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     }
     s_cnt[sq] = (unsigned short)min(nt, 65535);
     s_idle[sq] = (unsigned char)idle;
-    s_total[sq] = p.kv_len[sq];
-    s_tok[sq] = p.cu_q[sq];
+    s_total[sq] = total;
+    s_tok[sq] = tok;
   }
   __syncthreads();
   // a request's share of the common axis: per head block its tiles and the cost of a piece
@@ -492,6 +500,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       pdl_wait();
       waited = true;
     }
+    int new_slot = -1;
     if (!fused) {
       for (int id = threadIdx.x; id < 16 * CH; id += NCW * 32) {
         const int R = id / CH, cc = id - R * CH;
@@ -502,11 +511,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     } else {
       const bf16* row = fq.qkv + tok * fq.qkv_stride;
       const float* cs = nullptr;
-      if (fq.cos_sin) {
-        int pos = fq.positions[tok];
-        pos = pos < 0 ? 0 : (pos >= fq.max_position ? fq.max_position - 1 : pos);
-        cs = fq.cos_sin + (size_t)pos * fq.rotary_dim;
-      }
+      if (fq.cos_sin) cs = fq.cos_sin + (size_t)s_pos[seq] * fq.rotary_dim;
+      if (has_last && fq.store && g0 == 0) new_slot = fq.slot_mapping[tok];   // used behind the barrier below
       // warp 0: the new key, warp 1: the new value; asked for before the query heads, used behind them
       const bool has_new = has_last && fq.store && warp < 2;
       float nv[FVEC];
@@ -533,7 +539,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     consumer_sync();
     if (fused && has_last && fq.store && g0 == 0) {
       // one block per (request, KV head) stores the new key and value for the steps to come
-      const int slot = fq.slot_mapping[tok];
+      const int slot = new_slot;
       if (slot >= 0 && slot < p.n_pages * page_size) {
         const int pg = slot / page_size, off = slot - pg * page_size;
         for (int id = threadIdx.x; id < 2 * CH; id += NCW * 32) {
