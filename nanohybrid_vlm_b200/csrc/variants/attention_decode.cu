@@ -77,8 +77,14 @@ constexpr int Q_BYTES = 16 * D * 2;
 constexpr int merge_bytes(int mrows) { return NCW * mrows * D * 4 + NCW * mrows * 2 * 4; }
 constexpr int MAX_SEQS = 512;
 constexpr size_t smem_bytes(int stages, int mrows) { return 1024 + (size_t)stages * STAGE_BYTES + merge_bytes(mrows) + Q_BYTES; }
-static_assert(smem_bytes(STAGES_MIN, 16) + 11 * 1024 <= 227 * 1024 && smem_bytes(STAGES_DEEP, 8) + 11 * 1024 <= 227 * 1024,
-              "ring, merge buffer and queries must fit one block's shared memory");
+// what the kernel declares beside that: the new key and value, the rows copied ahead, the plan's numbers per request
+// (19 bytes each), barriers and flags
+constexpr size_t static_bytes(int stages, int mrows) {
+  return 2 * D * 2 + (mrows + 2) * D * 2 + D * 4 + (size_t)MAX_SEQS * 19 + 4 + stages * 20 + 64;
+}
+static_assert(smem_bytes(STAGES_MIN, 16) + static_bytes(STAGES_MIN, 16) <= 227 * 1024 &&
+                  smem_bytes(STAGES_DEEP, 8) + static_bytes(STAGES_DEEP, 8) <= 227 * 1024,
+              "ring, merge buffer, queries and the plan must fit one block's shared memory");
 constexpr int MIN_TILES = 4;
 // What a piece costs a block beside its tiles (the query heads' norm and rotation, the merge of the warps, the
 // output), in tiles' worth of time: the blocks' shares are equal in tiles + PIECE_COST per (request, head block),
@@ -110,6 +116,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(NCW * 32) : "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+// 16 bytes from global to shared memory without passing through registers; the thread goes on and asks later
+__device__ __forceinline__ void copy16_async(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_async_wait() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 // Element offset of (row, 16-byte chunk) in a tile of `ROWS` rows as TMA lays it out: one box of 64 columns after
 // the other, in a box rows of 128 bytes whose chunks are exchanged by chunk ^ (row & 7).
@@ -292,6 +303,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   float* mml = mo + NCW * MROWS * D;                                            // [NCW][MROWS][2]
   bf16* qbuf = reinterpret_cast<bf16*>(mml + NCW * MROWS * 2);                  // [16][D], chunks exchanged as in a tile
   __shared__ __align__(16) bf16 s_new[2][D];                  // the new token's key and value (fused form)
+  // fused form: the rows of qkv that the piece after the one at work needs, as they lie in qkv (the head block's
+  // query heads, then the new key and the new value), and the cosines and sines of its position
+  __shared__ __align__(16) bf16 s_raw[MROWS + 2][D];
+  __shared__ __align__(16) float s_raw_cs[D];
   __shared__ unsigned short s_cnt[MAX_SEQS];                 // tiles of each request (0: not a single-token request, or idle)
   __shared__ unsigned char s_idle[MAX_SEQS];                 // 1: an idle entry (a single token whose newest key has no page)
   __shared__ int s_prefix[MAX_SEQS + 1];
@@ -483,6 +498,24 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
   // ------------------------------------------------------------------ consumers
   bool waited = !early, ok = true;
   uint32_t gi_base = 0;
+  // Fused form: while a piece is at its tiles, the rows of qkv of the piece after it (and its cosines and sines) are
+  // copied to shared memory as they are, asynchronously, so that only a block's first piece waits for them.
+  bool raw_ready = false;                                    // s_raw and s_raw_cs hold the coming piece's rows
+  auto fetch_ahead = [&](const Piece& q) {
+    const int kvh = q.hb / chunks, g0 = (q.hb - kvh * chunks) * 16;
+    const int gn = min(rows_per, G - g0);
+    const bf16* row = fq.qkv + (size_t)s_tok[q.seq] * fq.qkv_stride;
+    const bool newest = fq.store && q.t_begin + q.n_tiles == q.nt;
+    for (int id = threadIdx.x; id < (gn + (newest ? 2 : 0)) * CH; id += NCW * 32) {
+      const int R = id / CH, cc = id - R * CH;
+      const int head = R < gn ? kvh * G + g0 + R : p.nq + (R == gn ? 0 : nkv) + kvh;
+      copy16_async(&s_raw[R < gn ? R : MROWS + (R - gn)][cc * 8], row + (size_t)head * D + cc * 8);
+    }
+    if (fq.cos_sin) {
+      const float* cs = fq.cos_sin + (size_t)s_pos[q.seq] * fq.rotary_dim;
+      for (int id = threadIdx.x; id < fq.rotary_dim / 4; id += NCW * 32) copy16_async(&s_raw_cs[id * 4], cs + id * 4);
+    }
+  };
   Cursor cur = cursor_at(u0);
   for (long long u = u0; u < u1;) {
     const Piece pc = next_piece(cur, u);
@@ -509,18 +542,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
         *reinterpret_cast<uint4*>(qbuf + tile_off<16>(R, cc)) = v;
       }
     } else {
+      // the token's row of qkv, or (any piece but the block's first) what was copied of it while the piece before was at work
       const bf16* row = fq.qkv + tok * fq.qkv_stride;
       const float* cs = nullptr;
-      if (fq.cos_sin) cs = fq.cos_sin + (size_t)s_pos[seq] * fq.rotary_dim;
+      if (fq.cos_sin) cs = raw_ready ? s_raw_cs : fq.cos_sin + (size_t)s_pos[seq] * fq.rotary_dim;
       if (has_last && fq.store && g0 == 0) new_slot = fq.slot_mapping[tok];   // used behind the barrier below
       // warp 0: the new key, warp 1: the new value; asked for before the query heads, used behind them
       const bool has_new = has_last && fq.store && warp < 2;
       float nv[FVEC];
-      if (has_new) head_load(nv, row + (size_t)(p.nq + (warp == 0 ? 0 : nkv) + kvh) * D, lane);
+      if (has_new) head_load(nv, raw_ready ? s_raw[MROWS + warp] : row + (size_t)(p.nq + (warp == 0 ? 0 : nkv) + kvh) * D, lane);
       for (int R = warp; R < 16; R += NCW) {                  // the query heads of the group dealt to the warps
         float v[FVEC];
         if (R < gn) {
-          fused_head(v, row + (size_t)(kvh * G + g0 + R) * D, fq.q_w, cs, fq, lane);
+          fused_head(v, raw_ready ? s_raw[R] : row + (size_t)(kvh * G + g0 + R) * D, fq.q_w, cs, fq, lane);
         } else {
 #pragma unroll
           for (int k = 0; k < FVEC; ++k) v[k] = 0.f;
@@ -537,6 +571,16 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       }
     }
     consumer_sync();
+    raw_ready = false;
+    if (fused && u < u1) {                                    // s_raw is free: the barrier above is behind its last reader
+      Cursor c2 = cur;
+      long long u2 = u;
+      const Piece nx = next_piece(c2, u2);
+      if (nx.n_tiles > 0) {
+        fetch_ahead(nx);
+        raw_ready = true;
+      }
+    }
     if (fused && has_last && fq.store && g0 == 0) {
       // one block per (request, KV head) stores the new key and value for the steps to come
       const int slot = new_slot;
@@ -702,6 +746,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
         if (threadIdx.x == 0) p.counters[unit] = 0;            // ready for the next launch
       }
     }
+    copies_async_wait();                                       // what this thread copied for the next piece has landed
     consumer_sync();                                           // the merge buffers and the query are reused by the next piece
   }
   if (!waited) pdl_wait();
@@ -769,6 +814,8 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
   p.fq = FusedQK{};
   if (qkv) {
     ATT_REQUIRE(qkv_stride % 8 == 0 && ((uintptr_t)qkv % 16) == 0, "attention: qkv must be 16-byte aligned");
+    ATT_REQUIRE(!cos_sin || (((uintptr_t)cos_sin % 16) == 0 && rotary_dim % 4 == 0),
+                "attention: the table of cosines and sines must be 16-byte aligned, its rows too");
     ATT_REQUIRE(!cos_sin || (positions && rotary_dim > 0 && rotary_dim <= D && rotary_dim % (2 * FVEC) == 0),
                 "attention: the fused decode form rotates in steps of %d elements, rotary_dim is %d", 2 * FVEC, rotary_dim);
     ATT_REQUIRE(!store || slot_mapping, "attention: storing the new keys needs the slot mapping");
