@@ -34,10 +34,15 @@
 // written) never reach a result: their scores are replaced, not added to, and their value rows are cleared in
 // shared memory before the product.
 //
+// What a piece costs beside its tiles is kept small: a block finds its first piece by a search and walks on from
+// there with a cursor; the plan leaves each request's key count, token row and position in shared memory.
+//
 // With `qkv` given the kernel works from the projection's output: it norms and rotates the new token's query and key
 // heads itself (the arithmetic and rounding of qk_norm_rope_store.cu), puts the new key and value into the tile that
 // holds the request's last keys, and one block per (request, KV head) stores them in the cache.  In that form the
-// producer starts fetching old keys before the kernel waits for its predecessor (programmatic dependent launch).
+// producer starts fetching old keys before the kernel waits for its predecessor (programmatic dependent launch), and
+// while a piece is at its tiles the rows of qkv and the cosines of the piece after it are copied to shared memory,
+// so that only a block's first piece waits for them.
 //
 // Every wait on an mbarrier is bounded; one that runs out sets the file's error word.
 #include <math.h>
