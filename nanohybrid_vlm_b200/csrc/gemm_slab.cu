@@ -68,6 +68,11 @@ struct alignas(64) Params {
   int nb;                // boxes of 64 columns per stage
   int ks;                // stages over K (K padded to ks * nb * 64 columns in the copy)
   int x3d;               // K is a multiple of 64: a stage's columns of x come in one copy
+  // a hint: the copy that the product after this one will read; block c asks its first bytes into L2 as it sends
+  // for its own last stage (null: no hint)
+  const unsigned char* next_slabs;
+  long long next_slab_bytes;
+  int next_bytes, next_blocks;
 };
 
 __global__ void __launch_bounds__(THREADS, 1) gemm_slab_kernel(const __grid_constant__ Params p) {
@@ -137,6 +142,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_slab_kernel(const __grid_cons
         if (NHV_UNIT_IS_SENT(i)) {
           issue_w(i);
           issue_x(i);
+        }
+      }
+      if (p.next_slabs && c < p.next_blocks) {
+        const unsigned char* nx = p.next_slabs + (size_t)c * p.next_slab_bytes;
+        for (int off = 0; off < p.next_bytes; off += 16384) {
+          const int n = min(16384, p.next_bytes - off);
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(nx + off), "r"(n) : "memory");
         }
       }
       if (!ok) give_up_delay();
@@ -266,8 +278,23 @@ NHV_API int nhv_gemm_slab_geometry(int N, int K, int mode, int sms, int* blocks,
 
 // slabs: the copy made by ops.slab_weight for exactly this geometry (nhv_gemm_slab_geometry with the same N, K,
 // mode and SM count).
+static int gemm_slab_launch(void* y, const void* x, const void* slabs, int M, int N, int K, int lda, int ldc, int mode,
+                            int sms, const void* next_slabs, long long next_slab_bytes, int next_bytes, int next_blocks,
+                            cudaStream_t stream);
 NHV_API int nhv_gemm_slab(void* y, const void* x, const void* slabs, int M, int N, int K, int lda, int ldc, int mode,
                           int sms, cudaStream_t stream) {
+  return gemm_slab_launch(y, x, slabs, M, N, K, lda, ldc, mode, sms, nullptr, 0, 0, 0, stream);
+}
+// The same with a hint: the copy (and its geometry: bytes per block, blocks) that the next product will read, of which
+// every block asks `next_bytes` into L2 when it has sent for its own last stage.
+NHV_API int nhv_gemm_slab_hint(void* y, const void* x, const void* slabs, int M, int N, int K, int lda, int ldc, int mode,
+                               int sms, const void* next_slabs, long long next_slab_bytes, int next_bytes, int next_blocks,
+                               cudaStream_t stream) {
+  return gemm_slab_launch(y, x, slabs, M, N, K, lda, ldc, mode, sms, next_slabs, next_slab_bytes, next_bytes, next_blocks, stream);
+}
+static int gemm_slab_launch(void* y, const void* x, const void* slabs, int M, int N, int K, int lda, int ldc, int mode,
+                            int sms, const void* next_slabs, long long next_slab_bytes, int next_bytes, int next_blocks,
+                            cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   NHV_REQUIRE(M > 0 && M <= X_ROWS, "gemm_slab: takes 1 to %d tokens, got %d", X_ROWS, M);
   NHV_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K && ldc >= N,
@@ -279,6 +306,10 @@ NHV_API int nhv_gemm_slab(void* y, const void* x, const void* slabs, int M, int 
   p.slabs = (const unsigned char*)slabs;
   p.y = y;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.mode = mode;
+  p.next_slabs = (const unsigned char*)next_slabs;
+  p.next_slab_bytes = next_slab_bytes;
+  p.next_bytes = next_bytes < next_slab_bytes ? next_bytes / 16 * 16 : (int)(next_slab_bytes / 16 * 16);
+  p.next_blocks = next_blocks;
   p.x3d = K % 64 == 0;
   NHV_REQUIRE(p.x3d ? make_x_map_3d(&p.x_map, x, M, K, lda, p.nb) : make_x_map(&p.x_map, x, M, K, lda),
               "gemm_slab: cannot encode the tensor map of x [%d, %d]", M, K);

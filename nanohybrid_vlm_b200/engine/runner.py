@@ -99,6 +99,7 @@ class ModelRunner:
             cfg.decode_weight_copy = need <= free // 4
         if not cfg.decode_weight_copy:
             return 0
+        ops.new_slab_family()            # this model's copies live and die together
         return sum(ops.prepare_streaming(w, m) for w, m in weights)
 
     # ------------------------------------------------------------------ sizing

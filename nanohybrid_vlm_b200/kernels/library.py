@@ -30,6 +30,7 @@ _SIGNATURES = {
     "nhv_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, P],
     "nhv_gemm_stream_k": [P, P, P, I, I, I, I, I, I, I, P, P, I, I, P],
     "nhv_gemm_slab": [P, P, P, I, I, I, I, I, I, I, P],
+    "nhv_gemm_slab_hint": [P, P, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P],
     "nhv_gemm_slab_geometry": [I, I, I, I, P, P, P, P, P],
     "nhv_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, I, P],
 }

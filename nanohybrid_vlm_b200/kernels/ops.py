@@ -9,6 +9,7 @@ that the 32-bit path never sees a reduced-precision matrix mode.
 """
 from __future__ import annotations
 
+import os
 import weakref
 
 import torch
@@ -372,8 +373,7 @@ def _small_m(out, x, weight, M: int, N: int, K: int, mode: int, up_row_offset: i
     tiles = -(-N // (32 if mode == 2 else 64))
     slab = _slabs.get(weight.data_ptr())
     if slab is not None and slab[0]() is weight and slab[2] == mode and M <= SLAB_MAX_M:
-        call("nhv_gemm_slab", out.data_ptr(), x.data_ptr(), slab[1].data_ptr(), M, N, K, x.stride(0), N, mode, sms,
-             stream_ptr())
+        _slab_product(out, x, slab[1], M, N, K, mode, sms)
         return
     if tiles > STREAM_K_COUNTERS:
         call("nhv_gemm_small_m", out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), N, mode,
@@ -383,6 +383,47 @@ def _small_m(out, x, weight, M: int, N: int, K: int, mode: int, up_row_offset: i
          up_row_offset, scratch.data_ptr(), counters.data_ptr(), STREAM_K_COUNTERS, sms, stream_ptr())
 
 
+def _slab_product(out, x, copy, M: int, N: int, K: int, mode: int, sms: int) -> None:
+    """The product from the per-SM copy, with a hint for the one after it.  A decode step runs the same products in
+    the same order every time, so each remembers which copy was read right after its own last time; its blocks then
+    ask the first bytes of that copy into L2 as they send for their own last stage, and the next product's ring
+    fills from L2 instead of HBM (measured on B200 over the four products of an 8B-sized layer: 72.1 -> 70.1 us).
+    Only a hint, and only between copies that were made together (``new_slab_family``: one model's copies live and
+    die together, so a captured launch never names memory that has been given back); a copy that is gone or unknown
+    gets none."""
+    global _slab_last
+    key = copy.data_ptr()
+    family = _slab_family.get(key)
+    if (_slab_last is not None and _slab_last != key and SLAB_HINT_BYTES and family is not None
+            and _slab_family.get(_slab_last) == family):
+        _slab_after[_slab_last] = (weakref.ref(copy), key, copy.numel() * copy.element_size())
+    _slab_last = key
+    hint = _slab_after.get(key)
+    nxt = hint[0]() if hint is not None else None
+    if nxt is not None and nxt.data_ptr() == hint[1] and nxt.numel() * nxt.element_size() == hint[2] and SLAB_HINT_BYTES:
+        blocks = min(sms, _slab_blocks.get(hint[1], 0))
+        if blocks > 0:
+            call("nhv_gemm_slab_hint", out.data_ptr(), x.data_ptr(), key, M, N, K, x.stride(0), N, mode, sms, hint[1],
+                 hint[2] // blocks, SLAB_HINT_BYTES, blocks, stream_ptr())
+            return
+    call("nhv_gemm_slab", out.data_ptr(), x.data_ptr(), key, M, N, K, x.stride(0), N, mode, sms, stream_ptr())
+
+
+# of the next product's copy, per block, asked into L2 ahead (0: no hints; NHV_SLAB_HINT_BYTES overrides it)
+SLAB_HINT_BYTES = int(os.environ.get("NHV_SLAB_HINT_BYTES", "65536"))
+_slab_after: dict = {}  # data pointer of a copy -> (weak reference to the copy read after it last time, its pointer, its bytes)
+_slab_blocks: dict = {} # data pointer of a copy -> the blocks that share it
+_slab_family: dict = {} # data pointer of a copy -> the family it was made in
+_family = 0
+
+
+def new_slab_family() -> None:
+    """The copies made from here on belong together (a model's: the runner says so before it makes them)."""
+    global _family
+    _family += 1
+
+
+_slab_last = None       # data pointer of the copy that the last product read
 SLAB_MAX_M = 8          # tokens that csrc/gemm_slab.cu takes
 _slabs: dict = {}       # data pointer of a weight matrix -> (weak reference to it, its copy for gemm_slab.cu, mode)
 
@@ -412,6 +453,9 @@ def prepare_streaming(weight: torch.Tensor, mode: int) -> int:
     if old is not None and old[0]() is weight and old[2] == mode:
         return 0
     copy = slab_weight(weight, mode, _sm_count(weight.device))
+    n = weight.shape[0] // 2 if mode == 2 else weight.shape[0]
+    _slab_blocks[copy.data_ptr()] = slab_geometry(n, weight.shape[1], mode, _sm_count(weight.device))["blocks"]
+    _slab_family[copy.data_ptr()] = _family
     _slabs[key] = (weakref.ref(weight), copy, mode)
     weakref.finalize(weight, _drop_slab, key, copy.data_ptr())
     return copy.numel() * copy.element_size()
@@ -421,6 +465,9 @@ def _drop_slab(key: int, copy_ptr: int) -> None:
     entry = _slabs.get(key)
     if entry is not None and entry[1].data_ptr() == copy_ptr:
         del _slabs[key]
+    _slab_blocks.pop(copy_ptr, None)
+    _slab_after.pop(copy_ptr, None)
+    _slab_family.pop(copy_ptr, None)
 
 
 def slab_geometry(N: int, K: int, mode: int, sms: int) -> dict:
