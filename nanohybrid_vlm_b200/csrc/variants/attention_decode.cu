@@ -718,30 +718,35 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
         constexpr int first_slot = 1;
         for (int id = threadIdx.x; id < gn * (D / 4); id += NCW * 32) {
           const int R = id / (D / 4), c4 = id - R * (D / 4);
-          float M = -INFINITY;
-          for (int k = 0; k < pieces; ++k) {
-            const size_t at = ((size_t)(first_owner + k) * 2 + (k == 0 ? first_slot : 0)) * 16;
-            M = fmaxf(M, __ldcg(p.part_ml + (at + R) * 2));
-          }
-          float L = 0.f;
+          // One pass, eight pieces' loads on their way at a time (the pieces lie in L2: what this costs is trips,
+          // not bytes): the running maximum moves with every eight, and what is summed so far is rescaled to it.
+          float M = -INFINITY, L = 0.f;
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int k0 = 0; k0 < pieces; k0 += 4) {             // four independent 16-byte loads in flight
-            float4 t[4];
-            float m[4], l[4];
+          for (int k0 = 0; k0 < pieces; k0 += 8) {
+            float4 t[8];
+            float2 ml[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 8; ++j) {
               const int k = min(k0 + j, pieces - 1);
               const size_t at = ((size_t)(first_owner + k) * 2 + (k == 0 ? first_slot : 0)) * 16;
               t[j] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (at + R) * D) + c4);
-              m[j] = __ldcg(p.part_ml + (at + R) * 2);
-              l[j] = __ldcg(p.part_ml + (at + R) * 2 + 1);
+              ml[j] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (at + R) * 2));     // (max, sum)
             }
+            float Mb = M;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (k0 + j >= pieces || m[j] == -INFINITY) continue;
-              const float f = exp2f(m[j] - M);
+            for (int j = 0; j < 8; ++j)
+              if (k0 + j < pieces) Mb = fmaxf(Mb, ml[j].x);
+            if (Mb == -INFINITY) continue;                     // nothing but pieces without a key so far
+            const float f0 = M == -INFINITY ? 0.f : exp2f(M - Mb);
+            acc.x *= f0; acc.y *= f0; acc.z *= f0; acc.w *= f0;
+            L *= f0;
+            M = Mb;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (k0 + j >= pieces || ml[j].x == -INFINITY) continue;
+              const float f = exp2f(ml[j].x - M);
               acc.x += t[j].x * f; acc.y += t[j].y * f; acc.z += t[j].z * f; acc.w += t[j].w * f;
-              L += l[j] * f;
+              L += ml[j].y * f;
             }
           }
           const float inv = L > 0.f ? 1.0f / L : 0.f;
