@@ -378,13 +378,16 @@ TMA_FUSED_SHAPES = [(32, 8, 128, 256, 0, 128, True), (2, 1, 256, 64, 40, 0, True
                     (3, 3, 128, 192, 0, 64, True)]
 
 
-@pytest.mark.parametrize("tma,nq,nkv,d,page,window,rot,norm", [(False, *s) for s in FUSED_SHAPES] + [(True, *s) for s in TMA_FUSED_SHAPES])
-def test_attention_decode_from_the_projection_output(ops, tma, nq, nkv, d, page, window, rot, norm):
+@pytest.mark.parametrize("tma,nq,nkv,d,page,window,rot,norm,many",
+                         [(False, *s, False) for s in FUSED_SHAPES] + [(True, *s, False) for s in TMA_FUSED_SHAPES]
+                         + [(True, *s, True) for s in TMA_FUSED_SHAPES[:4]])
+def test_attention_decode_from_the_projection_output(ops, tma, nq, nkv, d, page, window, rot, norm, many):
     """A step of single tokens: the decode kernel given qkv as the projection wrote it (it norms, rotates and
     stores by itself) against ``reference_attention`` over keys and values gathered from the cache, with the new
     query and key heads normed and rotated apart in float64 (the plain implementation's formulas); the cache
     afterwards holds the new keys and values and nothing else has changed; and again without storing, as a
-    layer that reads another layer's cache runs."""
+    layer that reads another layer's cache runs.  ``many``: 163 short requests instead of six, so that a block has
+    several pieces."""
     from types import SimpleNamespace
     from nanohybrid_vlm_b200.kernels import attention_decode
     assert attention_decode.supports(d, nq, nkv, page) == tma or not tma
@@ -392,6 +395,8 @@ def test_attention_decode_from_the_projection_output(ops, tma, nq, nkv, d, page,
     rng = np.random.default_rng(11)
     g = torch.Generator().manual_seed(11)
     lens = [611, 1, 64, 65, 200, 7]                          # keys of each request, the new token included
+    if many:    # every block of the persistent kernel has several pieces: the rows of qkv of all but its first are copied ahead
+        lens = rng.integers(1, 150, 160).tolist() + [611, 64, 65]
     S = len(lens)
     n_pages = sum(-(-L // page) for L in lens) + 3
     pages = (torch.randn(n_pages, 2, nkv, page, d, generator=g) * 0.5).to(torch.bfloat16)   # stale contents everywhere
